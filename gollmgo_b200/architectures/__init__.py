@@ -1,1 +1,2 @@
 from . import llama     # registers "LlamaForCausalLM"
+from . import tekenex   # registers "Tekenex"

@@ -4,8 +4,9 @@ group, and state slots.
 Layers are grouped by what they need of the cache.  A *paged* need is
 (kv heads, head size, window); layers with equal needs share one group: one page
 pool, one block table per request, one device tensor of shape
-``[layers of the group, 2 (k, v), pages, kv heads, page size, head size]``, so
-one page id addresses every layer of the group.  A group with a window gives a
+``[layers of the group, 2 (k, v), pages, kv heads, page size, head size]`` (one
+instead of 2 where keys and values are the same rows: ``shared_kv``), so one page
+id addresses every layer of the group.  A group with a window gives a
 page back as soon as every token in it is behind the window of all future
 queries.  A *fixed-state* need is a tensor shape per request; its buffer is
 indexed by the request's state slot.
@@ -30,6 +31,7 @@ class PagedKVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: all keys are kept
+    shared_kv: bool = False           # keys and values are one tensor (a latent both are expanded from)
 
 
 @dataclass(frozen=True)
@@ -99,8 +101,8 @@ class CacheManager:
         if device is not None:
             import torch
             for g in self.groups:
-                g.kv = torch.zeros(len(g.cache_ids), 2, num_pages, g.need.n_kv_heads, page_size,
-                                   g.need.head_dim, dtype=dtype, device=device)
+                g.kv = torch.zeros(len(g.cache_ids), 1 if g.need.shared_kv else 2, num_pages, g.need.n_kv_heads,
+                                   page_size, g.need.head_dim, dtype=dtype, device=device)
             for cid, need in self.state_needs.items():
                 self.state_buffers[cid] = torch.zeros(max_requests, *need.shape,
                                                       dtype=getattr(torch, need.dtype), device=device)
@@ -113,14 +115,15 @@ class CacheManager:
         total = 0
         for need in needs:
             if isinstance(need, PagedKVNeed):
-                total += 2 * need.n_kv_heads * need.head_dim * page_size * element_size
+                total += (1 if need.shared_kv else 2) * need.n_kv_heads * need.head_dim * page_size * element_size
         return total
 
     def layer_cache(self, cache_id: int):
-        """(k, v) tensors [pages, nkv, page, d] of one cache entry, and its group index."""
+        """(k, v) tensors [pages, nkv, page, d] of one cache entry, and its group index.  A group
+        whose keys and values are one tensor gives that tensor twice."""
         gi, idx = self.group_of[cache_id]
         g = self.groups[gi]
-        return g.kv[idx, 0], g.kv[idx, 1], gi
+        return g.kv[idx, 0], g.kv[idx, 0 if g.need.shared_kv else 1], gi
 
     def _give_back(self, gi: int, page: int) -> None:
         """Return a page of group gi to its pool.  With GOLLMGO_B200_POISON_FREED=1 its keys and

@@ -1,5 +1,5 @@
-"""One registry from the architecture's name (config.json ``architectures[0]``) to
-its model.  The reference has none: it never looks at ``architectures`` and runs
+"""One registry from the architecture's name (config.json ``architectures[0]``, or the
+string ``architecture``) to its model.  The reference has none: it never looks at ``architectures`` and runs
 any checkpoint with the right tensor names (cmd/gollmgo/gpu.go:91-92).
 
 An architecture is two functions: ``parse(config_dict) -> typed config`` and
@@ -34,6 +34,8 @@ def known_architectures():
 
 def resolve_architecture(config_dict: dict) -> Architecture:
     archs = config_dict.get("architectures")
+    if not archs and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]          # a file that names its one design in the singular
     if not archs:
         raise ConfigError("config.json: 'architectures' is missing; known: "
                           + ", ".join(known_architectures()))

@@ -1,0 +1,85 @@
+// The latent of a latent-attention mixer: one row per token from which every head's keys and
+// values are expanded, and the only thing its cache holds.
+//
+// gg_latent_norm_write: c[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w, x[t] = columns
+// [col0, col0 + R) of row t of the projection output; c goes, rounded to the cache's type, to
+// the paged cache [pages, 1, page_size, Rp] at slot_mapping[t] (Rp >= R: the columns past R are
+// written as zeros, so that a kernel which reads rows of Rp values sees R values and padding).
+// Statistics and the product with the weight are float32.
+//
+// gg_act: element-wise activations of a plain (ungated) feed-forward.
+#include "common.cuh"
+
+template <typename TA>
+__global__ void latent_norm_write_kernel(const TA* __restrict__ src, long long src_stride, int col0, int R,
+                                         int Rp, const float* __restrict__ w, float eps,
+                                         const int* __restrict__ slots, TA* __restrict__ cache) {
+  __shared__ float red[33];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int slot = slots[t];                       // the step's packed list: copied in before the step began
+  pdl_wait();
+  if (slot < 0) return;                            // padding of a captured step: nothing to keep
+  const TA* x = src + (size_t)t * src_stride + col0;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    const float v = to_f32(x[c]);
+    ss += v * v;
+  }
+  const float rinv = rsqrtf(block_sum(ss, red) / (float)R + eps);
+  TA* o = cache + (size_t)slot * Rp;
+  for (int c = threadIdx.x; c < Rp; c += blockDim.x)
+    o[c] = c < R ? from_f32<TA>(to_f32(x[c]) * rinv * w[c]) : from_f32<TA>(0.f);
+}
+
+extern "C" int gg_latent_norm_write(const void* src, long long src_stride, int col0, int R, int Rp,
+                                    const float* w, float eps, const int* slots, void* cache,
+                                    int act_dtype, int T, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && R > 0 && Rp >= R && col0 >= 0 && src_stride >= col0 + R,
+             "latent_norm_write: bad sizes T=%d R=%d Rp=%d col0=%d stride=%lld", T, R, Rp, col0, src_stride);
+  GG_REQUIRE(src && w && slots && cache, "latent_norm_write: a pointer is null");
+  if (T == 0) return GG_OK;
+  const int threads = R >= 512 ? 256 : 128;
+  if (act_dtype == GG_F32)
+    gg_launch(latent_norm_write_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)src, src_stride, col0,
+              R, Rp, w, eps, slots, (float*)cache);
+  else if (act_dtype == GG_BF16)
+    gg_launch(latent_norm_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)src,
+              src_stride, col0, R, Rp, w, eps, slots, (__nv_bfloat16*)cache);
+  else
+    return gg_fail(GG_ERR_INVALID, "latent_norm_write: unknown dtype %d", act_dtype);
+  return gg_check_launch("latent_norm_write");
+}
+
+// kind 0: relu(z)^2;  1: gelu, tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));  2: silu
+enum { GG_ACT_RELU2 = 0, GG_ACT_GELU_TANH = 1, GG_ACT_SILU = 2 };
+
+__device__ __forceinline__ float act_apply(float z, int kind) {
+  if (kind == GG_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (kind == GG_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
+template <typename TA>
+__global__ void act_kernel(const TA* __restrict__ in, TA* __restrict__ out, size_t n, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+    out[e] = from_f32<TA>(act_apply(to_f32(in[e]), kind));
+}
+
+extern "C" int gg_act(const void* in, void* out, int act_dtype, long long n, int kind, cudaStream_t stream) {
+  GG_REQUIRE(n >= 0 && in && out, "act: bad arguments");
+  GG_REQUIRE(kind >= 0 && kind <= 2, "act: unknown activation %d", kind);
+  if (n == 0) return GG_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (act_dtype == GG_F32)
+    gg_launch(act_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)in, (float*)out, (size_t)n, kind);
+  else if (act_dtype == GG_BF16)
+    gg_launch(act_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in,
+              (__nv_bfloat16*)out, (size_t)n, kind);
+  else
+    return gg_fail(GG_ERR_INVALID, "act: unknown dtype %d", act_dtype);
+  return gg_check_launch("act");
+}

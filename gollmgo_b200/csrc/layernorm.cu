@@ -1,0 +1,167 @@
+// Norms with a mean and a bias, and the norm that sits on a sublayer's OUTPUT.
+//
+//   layer norm:  n(x) = (x - mean(x)) / sqrt(mean((x - mean)^2) + eps) * w + b
+//   rms norm:    n(x) = x / sqrt(mean(x^2) + eps) * w                     (layer = 0, b = null)
+//
+// gg_add_norm:        x = resid[r] (+ delta[r]); out[i] = TA(n(x))        (the norm ahead of a product
+//                     or of the head; r = rows ? rows[i] : i)
+// gg_norm_scale_add:  resid[t] += scale * n(y[t]);  copy[t] = TA(resid[t])
+//                     (a block that norms what a sublayer returns, scales it per channel and adds it
+//                     to the residual stream; the next sublayer reads the stream itself, so its
+//                     rounding to the activation type is made here too)
+//
+// Statistics, the affine part, the scaling and the residual sum are float32; the variance is
+// taken about the mean in a second pass over the row held in shared memory.
+#include "common.cuh"
+
+template <typename TA>
+__global__ void add_norm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                const float* __restrict__ w, const float* __restrict__ b,
+                                TA* __restrict__ out, const int* __restrict__ rows, int H, float eps,
+                                int write_back, int layer) {
+  extern __shared__ __align__(16) float xs[];          // H floats + 33 for the reduction
+  float* red = xs + H;
+  pdl_trigger();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  pdl_wait();
+  float* xr = resid + (size_t)r * H;
+  const TA* dr = delta ? delta + (size_t)r * H : nullptr;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float x = xr[c];
+    if (dr) {
+      x += to_f32(dr[c]);
+      if (write_back) xr[c] = x;
+    }
+    xs[c] = x;
+    s += x;
+  }
+  const float mean = layer ? block_sum(s, red) / (float)H : 0.f;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float dx = xs[c] - mean;
+    ss += dx * dx;
+  }
+  const float rinv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  TA* o = out + (size_t)i * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float n = (xs[c] - mean) * rinv * w[c];
+    if (b) n += b[c];
+    o[c] = from_f32<TA>(n);
+  }
+}
+
+template <typename TA>
+__global__ void norm_scale_add_kernel(float* __restrict__ resid, const TA* __restrict__ y,
+                                      const float* __restrict__ w, const float* __restrict__ b,
+                                      const float* __restrict__ scale, TA* __restrict__ copy, int H,
+                                      float eps, int layer) {
+  extern __shared__ __align__(16) float xs[];
+  float* red = xs + H;
+  pdl_trigger();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  const TA* yr = y + t * H;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float x = to_f32(yr[c]);
+    xs[c] = x;
+    s += x;
+  }
+  const float mean = layer ? block_sum(s, red) / (float)H : 0.f;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float dx = xs[c] - mean;
+    ss += dx * dx;
+  }
+  const float rinv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  float* xr = resid + t * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float n = (xs[c] - mean) * rinv * w[c];
+    if (b) n += b[c];
+    if (scale) n *= scale[c];
+    const float v = xr[c] + n;
+    xr[c] = v;
+    if (copy) copy[t * H + c] = from_f32<TA>(v);
+  }
+}
+
+// copy[t] = TA(resid[t]): the rows a sublayer reads when it takes the residual stream itself.
+template <typename TA>
+__global__ void cast_rows_kernel(const float* __restrict__ resid, TA* __restrict__ copy, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+    copy[e] = from_f32<TA>(resid[e]);
+}
+
+static int norm_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+template <typename K> static int norm_smem(K kernel, size_t smem, const char* who) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
+  }
+  return GG_OK;
+}
+
+extern "C" int gg_add_norm(float* resid, const void* delta, const float* w, const float* b, void* out,
+                           int act_dtype, const int* rows, int n, int H, float eps, int write_back,
+                           int layer, cudaStream_t stream) {
+  GG_REQUIRE(n >= 0 && H > 0 && eps >= 0.f, "add_norm: bad sizes n=%d H=%d eps=%g", n, H, (double)eps);
+  GG_REQUIRE(resid && w && out, "add_norm: residual, weight and output are needed");
+  if (n == 0) return GG_OK;
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  GG_REQUIRE(smem <= 227 * 1024, "add_norm: width %d needs %zu B of shared memory", H, smem);
+  int rc;
+  if (act_dtype == GG_F32) {
+    if ((rc = norm_smem(add_norm_kernel<float>, smem, "add_norm"))) return rc;
+    gg_launch(add_norm_kernel<float>, dim3(n), dim3(norm_threads(H)), smem, stream, resid, (const float*)delta, w, b,
+              (float*)out, rows, H, eps, write_back, layer);
+  } else if (act_dtype == GG_BF16) {
+    if ((rc = norm_smem(add_norm_kernel<__nv_bfloat16>, smem, "add_norm"))) return rc;
+    gg_launch(add_norm_kernel<__nv_bfloat16>, dim3(n), dim3(norm_threads(H)), smem, stream, resid,
+              (const __nv_bfloat16*)delta, w, b, (__nv_bfloat16*)out, rows, H, eps, write_back, layer);
+  } else {
+    return gg_fail(GG_ERR_INVALID, "add_norm: unknown dtype %d", act_dtype);
+  }
+  return gg_check_launch("add_norm");
+}
+
+extern "C" int gg_norm_scale_add(float* resid, const void* y, const float* w, const float* b,
+                                 const float* scale, void* copy, int act_dtype, int T, int H, float eps,
+                                 int layer, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && eps >= 0.f, "norm_scale_add: bad sizes T=%d H=%d eps=%g", T, H, (double)eps);
+  GG_REQUIRE(resid && y && w, "norm_scale_add: residual, input and weight are needed");
+  if (T == 0) return GG_OK;
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  GG_REQUIRE(smem <= 227 * 1024, "norm_scale_add: width %d needs %zu B of shared memory", H, smem);
+  int rc;
+  if (act_dtype == GG_F32) {
+    if ((rc = norm_smem(norm_scale_add_kernel<float>, smem, "norm_scale_add"))) return rc;
+    gg_launch(norm_scale_add_kernel<float>, dim3(T), dim3(norm_threads(H)), smem, stream, resid, (const float*)y, w, b,
+              scale, (float*)copy, H, eps, layer);
+  } else if (act_dtype == GG_BF16) {
+    if ((rc = norm_smem(norm_scale_add_kernel<__nv_bfloat16>, smem, "norm_scale_add"))) return rc;
+    gg_launch(norm_scale_add_kernel<__nv_bfloat16>, dim3(T), dim3(norm_threads(H)), smem, stream, resid,
+              (const __nv_bfloat16*)y, w, b, scale, (__nv_bfloat16*)copy, H, eps, layer);
+  } else {
+    return gg_fail(GG_ERR_INVALID, "norm_scale_add: unknown dtype %d", act_dtype);
+  }
+  return gg_check_launch("norm_scale_add");
+}
+
+extern "C" int gg_cast_rows(const float* resid, void* copy, int act_dtype, long long n, cudaStream_t stream) {
+  GG_REQUIRE(n >= 0 && resid && copy, "cast_rows: bad arguments");
+  if (n == 0) return GG_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act_dtype == GG_F32)
+    gg_launch(cast_rows_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, resid, (float*)copy, (size_t)n);
+  else if (act_dtype == GG_BF16)
+    gg_launch(cast_rows_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, resid, (__nv_bfloat16*)copy, (size_t)n);
+  else
+    return gg_fail(GG_ERR_INVALID, "cast_rows: unknown dtype %d", act_dtype);
+  return gg_check_launch("cast_rows");
+}

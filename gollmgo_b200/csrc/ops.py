@@ -489,3 +489,128 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torc
         raise KernelError("sample: seeds and draw indices must be int64")
     _check(lib().gg_sample(_p(logits), R, V, _p(temperature), _p(top_k), _p(top_p), _p(seeds),
                            _p(draw_index), _p(out), _stream()))
+
+
+# ---------------------------------------------------------------- norms with mean and bias, norms on a sublayer's output
+def add_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+             bias: Optional[torch.Tensor], out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+             write_back: bool = True, layer: bool = True) -> None:
+    """x = resid[r] (+ delta[r]); out[i] = norm(x), r = rows[i] if rows is given else i.
+    ``layer``: (x - mean) / sqrt(var + eps) * weight + bias; else x / sqrt(mean(x^2) + eps) * weight."""
+    _cuda(resid, delta, weight, bias, out, rows)
+    H = resid.shape[-1]
+    n = rows.numel() if rows is not None else out.shape[0]
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != H \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != H)):
+        raise KernelError("add_norm: residual, weight and bias must be float32 of one width")
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("add_norm: delta and out differ in dtype")
+    _check(lib().gg_add_norm(_p(resid), _p(delta), _p(weight), _p(bias), _p(out), dtype_code(out.dtype), _p(rows),
+                             n, H, ctypes.c_float(eps), int(write_back), int(layer), _stream()))
+
+
+def norm_scale_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                   scale: Optional[torch.Tensor], copy: Optional[torch.Tensor], eps: float, layer: bool = True) -> None:
+    """resid[t] += scale * norm(y[t]) (scale per channel, or none); copy[t] = resid[t] rounded to
+    copy's dtype, if given.  resid float32 [T, H]; y and copy of one dtype."""
+    _cuda(resid, y, weight, bias, scale, copy)
+    T, H = y.shape
+    if resid.dtype != torch.float32 or resid.shape[-1] != H or weight.dtype != torch.float32 or weight.numel() != H:
+        raise KernelError("norm_scale_add: residual and weight must be float32 of the input's width")
+    for v in (bias, scale):
+        if v is not None and (v.dtype != torch.float32 or v.numel() != H):
+            raise KernelError("norm_scale_add: bias and scale must be float32 of the input's width")
+    if copy is not None and (copy.dtype != y.dtype or copy.shape != y.shape):
+        raise KernelError("norm_scale_add: the copy has the input's shape and dtype")
+    _check(lib().gg_norm_scale_add(_p(resid), _p(y), _p(weight), _p(bias), _p(scale), _p(copy), dtype_code(y.dtype),
+                                   T, H, ctypes.c_float(eps), int(layer), _stream()))
+
+
+def cast_rows(resid: torch.Tensor, copy: torch.Tensor) -> None:
+    """copy = resid rounded to copy's dtype (float32 [T, H] in)."""
+    _cuda(resid, copy)
+    if resid.dtype != torch.float32 or resid.numel() != copy.numel():
+        raise KernelError("cast_rows: float32 in, as many elements out")
+    _check(lib().gg_cast_rows(_p(resid), _p(copy), dtype_code(copy.dtype), ctypes.c_longlong(copy.numel()), _stream()))
+
+
+ACT_KINDS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def act(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = activation(x), element by element: relu2 (the square of relu), gelu_tanh, silu."""
+    _cuda(x, out)
+    if x.dtype != out.dtype or x.numel() != out.numel() or kind not in ACT_KINDS:
+        raise KernelError(f"act: in and out of one dtype and size, kind one of {sorted(ACT_KINDS)}")
+    _check(lib().gg_act(_p(x), _p(out), dtype_code(x.dtype), ctypes.c_longlong(x.numel()), ACT_KINDS[kind], _stream()))
+
+
+# ---------------------------------------------------------------- latent attention
+def latent_norm_write(src: torch.Tensor, col0: int, rank: int, weight: torch.Tensor, eps: float,
+                      slot_mapping: torch.Tensor, cache: torch.Tensor) -> None:
+    """c[t] = rmsnorm(src[t, col0 : col0 + rank]) * weight, written to the paged cache
+    [pages, 1, page, rank_padded] at slot_mapping[t] (padding columns zero; slot < 0: no write)."""
+    _cuda(src, weight, slot_mapping, cache)
+    if weight.dtype != torch.float32 or weight.numel() != rank or cache.dtype != src.dtype:
+        raise KernelError("latent_norm_write: weight float32 [rank], cache of the source's dtype")
+    _check(lib().gg_latent_norm_write(_p(src), ctypes.c_longlong(src.stride(0)), col0, rank, cache.shape[-1],
+                                      _p(weight), ctypes.c_float(eps), _p(slot_mapping), _p(cache),
+                                      dtype_code(src.dtype), src.shape[0], _stream()))
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, k: int, groups: int, *,
+                 a_group_cols: int = 0, o_group_cols: int = 0, n_padded: Optional[int] = None,
+                 offsets: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None, row_div: int = 1,
+                 rows: Optional[int] = None, gated: bool = False, gate: Optional[torch.Tensor] = None,
+                 gate_col0: int = 0) -> None:
+    """out_g = a_g @ w_g^T for every group g (csrc/grouped_gemm.cu).  w [groups, n (2n if gated), k].
+    Without ``offsets`` every group has the first ``rows`` rows of a and reads columns
+    g * a_group_cols .. + k of them; with ``offsets`` [groups + 1] group g has rows offsets[g] ..
+    offsets[g + 1] of the row list (``rows`` = its length), row r reading row row_index[r] // row_div
+    of a.  Results go to out[r, g * o_group_cols : + n_padded] (zeros past n).  ``gate``: row r of
+    group g is multiplied by sigmoid(gate[a row, gate_col0 + g])."""
+    _cuda(w, offsets, row_index)
+    if a.dtype != w.dtype or out.dtype != a.dtype or a.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError("grouped_gemm: a, w and out of one dtype, rows contiguous")
+    if w.numel() != groups * (2 if gated else 1) * n * k:
+        raise KernelError("grouped_gemm: w does not hold groups x n x k values")
+    M = int(rows if rows is not None else a.shape[0])
+    _check(lib().gg_grouped_gemm(_p(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_cols), _p(row_index),
+                                 int(row_div), _p(w), _p(out), ctypes.c_longlong(out.stride(0)),
+                                 ctypes.c_longlong(o_group_cols), _p(offsets), M, groups, n, k,
+                                 int(n_padded if n_padded is not None else n), int(gated), _p(gate),
+                                 ctypes.c_longlong(gate.stride(0) if gate is not None else 0), int(gate_col0),
+                                 dtype_code(a.dtype), _stream()))
+
+
+# ---------------------------------------------------------------- mixture of experts
+MOE_MAX_EXPERTS, MOE_MAX_TOP = 1024, 32
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+              idx: torch.Tensor, wgt: torch.Tensor) -> None:
+    """Float32 logits h @ w_router^T + bias; idx [T, top] int32 = the largest, wgt [T, top]
+    float32 = softmax over those."""
+    _cuda(h, w_router, bias, idx, wgt)
+    T, D = h.shape
+    E = w_router.shape[0]
+    if w_router.dtype != h.dtype or w_router.shape[1] != D or idx.dtype != torch.int32 or wgt.dtype != torch.float32 \
+            or (bias is not None and bias.dtype != torch.float32):
+        raise KernelError("moe_route: router of the rows' dtype, bias and weights float32, choices int32")
+    _check(lib().gg_moe_route(_p(h), _p(w_router), _p(bias), T, D, E, top, _p(idx), _p(wgt), dtype_code(h.dtype), _stream()))
+
+
+def moe_align(idx: torch.Tensor, n: int, experts: int, offsets: torch.Tensor, order: torch.Tensor,
+              place: torch.Tensor) -> None:
+    """The n (token, choice) pairs of idx sorted by expert: offsets [experts + 1], order [n] (pair
+    index at each place), place [n] (place of each pair)."""
+    _cuda(idx, offsets, order, place)
+    _check(lib().gg_moe_align(_p(idx), n, experts, _p(offsets), _p(order), _p(place), _stream()))
+
+
+def moe_combine(y: torch.Tensor, place: torch.Tensor, wgt: torch.Tensor, shared: Optional[torch.Tensor],
+                out: torch.Tensor, top: int) -> None:
+    """out[t] = sum_j wgt[t, j] * y[place[t * top + j]] (+ shared[t])."""
+    _cuda(y, place, wgt, shared, out)
+    T, D = out.shape
+    _check(lib().gg_moe_combine(_p(y), _p(place), _p(wgt), _p(shared), _p(out), T, D, top, dtype_code(out.dtype), _stream()))

@@ -54,7 +54,8 @@ class ModelRunner:
         self.config, self.spec, self.model = build_model(config_dict, ctx)
         manifest = self.model.manifest()
         if weights is not None:
-            get = checkpoint_source(weights, manifest, self.dtype, self.device)
+            get = checkpoint_source(weights, manifest, self.dtype, self.device,
+                                    ignorable=self.spec.ignorable_tensors)
         elif weights_seed is not None:
             get = random_source(manifest, weights_seed, self.device, self.dtype)
         else:

@@ -1,4 +1,4 @@
-from . import attention, block, feed_forward, norm, position     # registers the built-in parts
+from . import attention, block, feed_forward, latent_attention, moe, norm, position     # registers the built-in parts
 from .context import BuildContext, QueryTiles, StepFacts, Workspace
 from .linear import linear, set_matmul_precision
 from .model import DecoderModel, build_model, manifest_for_config

@@ -5,11 +5,16 @@ residual stream x in float32.
 Each residual add is fused into the norm that follows it, so a block takes the
 residual and a pending delta (what the previous block still owes the residual)
 and returns its own pending delta.
+
+"post_norm": x += s1 * norm(mixer(x)); x += s2 * norm(ffn(x)): the norm on the
+sublayer's output, an optional per-channel scale, the sublayers reading x itself.
 """
 from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
+from ..weights import WeightSpec
 from .linear import NextNorm, NormedRows
 from .registry import register_block
 
@@ -71,4 +76,73 @@ class PreNormBlock:
         return self.feed_forward.forward(h, batch)
 
 
+class ResidualRows:
+    """What a block hands on when it has already added everything to the residual stream:
+    ``rows`` is the stream rounded to the activation type (the stream itself in the float32
+    mode), ready for a sublayer that reads the stream."""
+
+    def __init__(self, rows):
+        self.rows = rows
+
+
+class PostNormBlock:
+    """x += s1 * norm1(mixer(x)); x += s2 * norm2(ff(x)): the sublayers read the residual stream
+    itself and the norms sit on what they return.  s1, s2 are per-channel scales ("layer scale":
+    tensors ``scale_names`` under the layer's block prefix) or absent.  A layer without a
+    feed-forward stops after the first line.  params: layer_scale (bool), scale_names (two names).
+
+    Norm, scale, the add to the float32 stream and the stream's rounding for the next sublayer are
+    one kernel (csrc/layernorm.cu); any norm that offers ``norm_scale_add`` can be used."""
+
+    def __init__(self, layer_spec, mixer, feed_forward, mixer_norm, ffn_norm, ctx):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
+        self.ctx = ctx
+        self.hidden = mixer_norm.size
+        p = layer_spec.block
+        self.layer_scale = bool(p.get("layer_scale", False))
+        self.scale_names = tuple(p.get("scale_names", ("ls1", "ls2")))
+        self.scale1 = self.scale2 = None
+        for n in (mixer_norm, ffn_norm):
+            if n is not None and not hasattr(n, "norm_scale_add"):
+                raise TypeError(f"norm {type(n).__name__} cannot sit on a sublayer's output (no norm_scale_add)")
+        if feed_forward is not None and ffn_norm is None:
+            raise ValueError("a post-norm block with a feed-forward needs its norm")
+        if ctx.act_dtype != torch.float32:
+            ctx.workspace.reserve("stream_rows", ctx.max_tokens * self.hidden, ctx.act_dtype)
+
+    def weights(self):
+        if not self.layer_scale:
+            return {}
+        names = self.scale_names if self.feed_forward is not None else self.scale_names[:1]
+        return {n: WeightSpec((self.hidden,)) for n in names}
+
+    def load(self, get):
+        if self.layer_scale:
+            self.scale1 = get(self.scale_names[0]).to(torch.float32).contiguous()
+            if self.feed_forward is not None:
+                self.scale2 = get(self.scale_names[1]).to(torch.float32).contiguous()
+
+    def forward(self, resid, delta, batch, cache, writes_cache=True):
+        T = resid.shape[0]
+        f32 = self.ctx.act_dtype == torch.float32
+        if isinstance(delta, ResidualRows):
+            h = delta.rows
+        else:
+            if delta is not None:
+                raise ValueError("a post-norm block cannot take a pending delta from the block before it")
+            h = resid
+            if not f32:
+                h = self.ctx.workspace.get("stream_rows", T, self.hidden)
+                ops.cast_rows(resid, h)
+        nxt = resid if f32 else h                    # where the stream's rounded copy goes: over the rows just read
+        y = self.mixer.forward(h, batch, cache, writes_cache)
+        self.mixer_norm.norm_scale_add(resid, y, self.scale1, None if f32 else nxt)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(nxt, batch)
+            self.ffn_norm.norm_scale_add(resid, y, self.scale2, None if f32 else nxt)
+        return ResidualRows(nxt)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("post_norm", PostNormBlock)

@@ -13,7 +13,8 @@ from .registry import register_feed_forward
 
 
 class GatedMLP:
-    """params: hidden_size, intermediate_size, activation ("silu")."""
+    """params: hidden_size, intermediate_size, activation ("silu"), names (optional: the local
+    names of the gate, up and down tensors; default the Llama checkpoint's)."""
 
     def __init__(self, spec, ctx):
         self.ctx = ctx
@@ -22,6 +23,7 @@ class GatedMLP:
         act = spec.get("activation", "silu")
         if act != "silu":
             raise ValueError(f"activation {act!r} is not supported (known: silu)")
+        self.names = tuple(spec.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         ws, T = ctx.workspace, ctx.max_tokens
         ws.reserve("gate_up", T * 2 * self.inter, ctx.act_dtype)
         ws.reserve("ffn_act", T * self.inter, ctx.act_dtype)
@@ -30,15 +32,16 @@ class GatedMLP:
         self.w_down = None
 
     def weights(self):
-        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        g, u, d = self.names
+        return {g: WeightSpec((self.inter, self.hidden)),
+                u: WeightSpec((self.inter, self.hidden)),
+                d: WeightSpec((self.hidden, self.inter))}
 
     def load(self, get):
-        g, u = get("gate_proj.weight"), get("up_proj.weight")
+        g, u = get(self.names[0]), get(self.names[1])
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
-        self.w_down = get("down_proj.weight").contiguous()
+        self.w_down = get(self.names[2]).contiguous()
 
     # the optional protocol of parts/linear.py: the first product can take a norm's unnormalised
     # input, the last one can do the residual add and prepare the next norm
@@ -69,4 +72,41 @@ class GatedMLP:
         return linear(a, self.w_down, y, then)
 
 
+class PlainMLP:
+    """down(act(up(x))), no gate, no biases.  params: hidden_size, intermediate_size, activation
+    ("relu2" = the square of relu, "gelu_tanh", "silu"), names (local names of the up and down
+    tensors)."""
+
+    def __init__(self, spec, ctx):
+        self.ctx = ctx
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu2")
+        if self.activation not in ops.ACT_KINDS:
+            raise ValueError(f"activation {self.activation!r} is not supported (known: {sorted(ops.ACT_KINDS)})")
+        self.names = tuple(spec.get("names") or ("up", "down"))
+        ws, T = ctx.workspace, ctx.max_tokens
+        ws.reserve("ffn_up", T * self.inter, ctx.act_dtype)
+        ws.reserve("ffn_out", T * self.hidden, ctx.act_dtype)
+        self.w_up = None
+        self.w_down = None
+
+    def weights(self):
+        return {self.names[0]: WeightSpec((self.inter, self.hidden)),
+                self.names[1]: WeightSpec((self.hidden, self.inter))}
+
+    def load(self, get):
+        self.w_up = get(self.names[0]).contiguous()
+        self.w_down = get(self.names[1]).contiguous()
+
+    def forward(self, x, batch):
+        T = x.shape[0]
+        ws = self.ctx.workspace
+        u = ws.get("ffn_up", T, self.inter)
+        linear(x, self.w_up, u)
+        ops.act(u, u, self.activation)
+        return linear(u, self.w_down, ws.get("ffn_out", T, self.hidden))
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("mlp", PlainMLP)

@@ -1,0 +1,167 @@
+"""Latent attention: every head's keys and values are expanded from one low-rank row per token
+(the latent), which is all the cache keeps.  No position encoding.
+
+    q = Wq x  (heads x dim);   c = rmsnorm(Wdkv x) * w  (rank);   k_h = Wuk_h c;   v_h = Wuv_h c
+    out = Wo concat_h( sigmoid(Wg x)_h * softmax_j(scale q_h . k_hj) v_hj ),  j <= i
+
+The cache is a paged group with one "kv head" of size rank whose keys and values are the same
+rows (``PagedKVNeed(shared_kv=True)``), so the engine's paged attention kernels run it as they
+run a multi-query layer, in the latent's space: q_h . k_hj = (Wuk_h^T q_h) . c_j, and the sum of
+p_j v_hj is Wuv_h (sum p_j c_j).  The two per-head products around the attention are one grouped
+product each (csrc/grouped_gemm.cu; the second one applies the head's gate), the latent's norm
+and its write to the cache one kernel (csrc/latent.cu).  q, the latent and the gates come from
+one product with the three weights stacked.
+
+params: hidden_size, num_heads, head_dim (of q and k), v_head_dim, kv_rank, scale, eps (of the
+latent's norm), gate (bool), names: dict of the tensors' local names.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import PagedKVNeed
+from ..csrc import ops
+from ..weights import WeightSpec
+from .attention import ATTN_POLICY, TILES_GENERAL, TILES_MMA, TILES_TC, context_tiles, decode_splits, TILE_KEYS, MAX_TILES
+from .linear import linear
+from .registry import register_mixer
+
+DEFAULT_NAMES = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
+RANK_ALIGN = 16          # the latent's rows are padded to a multiple of this in the cache (zeros)
+
+
+class LatentAttention:
+    def __init__(self, spec, ctx):
+        self.ctx = ctx
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.dim = int(spec["head_dim"])
+        self.vdim = int(spec["v_head_dim"])
+        self.rank = int(spec["kv_rank"])
+        self.scale = float(spec["scale"])
+        self.eps = float(spec["eps"])
+        self.gated = bool(spec.get("gate", True))
+        self.names = {**DEFAULT_NAMES, **(spec.get("names") or {})}
+        self.rank_p = -(-self.rank // RANK_ALIGN) * RANK_ALIGN
+        if self.rank_p > 256:
+            raise ValueError(f"a latent of {self.rank} values is beyond what the attention kernels take as a head (256)")
+        # columns of the stacked first product: q | latent | gates, each start a multiple of 8
+        a8 = lambda n: -(-n // 8) * 8
+        self.col_c = a8(self.nh * self.dim)
+        self.col_g = self.col_c + a8(self.rank)
+        self.width1 = self.col_g + (a8(self.nh) if self.gated else 0)
+        self.num_sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count \
+            if ctx.device.type == "cuda" else 148
+        ws, T = ctx.workspace, ctx.max_tokens
+        ws.reserve("lat_proj", T * self.width1, ctx.act_dtype)
+        ws.reserve("lat_q", T * self.nh * self.rank_p, ctx.act_dtype)
+        ws.reserve("lat_o", T * self.nh * self.rank_p, ctx.act_dtype)
+        ws.reserve("attn_out", T * self.nh * self.vdim, ctx.act_dtype)
+        ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
+        self._ctas_per_split = -(-self.nh // 16)
+        self._cluster_cap = None
+        if ctx.device.type == "cuda":
+            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.rank_p, s, self.nh)
+                                       for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
+        esize = torch.empty((), dtype=ctx.act_dtype).element_size()
+        self._tile_bytes = TILE_KEYS * self.rank_p * esize
+        rows = max(n * self._splits(n, TILE_KEYS << b) for n in range(1, ctx.max_seqs + 1)
+                   for b in range(MAX_TILES.bit_length()))
+        ws.reserve("attn_part_o", rows * self.nh * self.rank_p, torch.float32)
+        ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
+        self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = None
+
+    def cache_need(self):
+        return PagedKVNeed(1, self.rank_p, None, shared_kv=True)
+
+    def _fast(self):
+        return self.ctx.act_dtype == torch.bfloat16 and self.rank_p in (64, 128) and ATTN_POLICY != "general"
+
+    def query_tiles(self):
+        need = [TILES_GENERAL]
+        if self._fast():
+            need.append(TILES_MMA)
+            if ATTN_POLICY == "auto" and self.nh % 2 == 0:
+                need.append(TILES_TC)
+        return need
+
+    def _splits(self, n_dec, max_context):
+        return decode_splits(n_dec, self._ctas_per_split, self.num_sms, self._cluster_cap,
+                             context_tiles(max_context), self._tile_bytes)
+
+    def step_tags(self, facts):
+        n = facts.num_seqs if facts.decode_only else 0
+        return (f"latent_slices={self._splits(n, facts.max_context)}",) if n else ()
+
+    def weights(self):
+        n, H = self.names, self.hidden
+        m = {n["q"]: WeightSpec((self.nh * self.dim, H)),
+             n["dkv"]: WeightSpec((self.rank, H)),
+             n["dkv_norm"]: WeightSpec((self.rank,)),
+             n["uk"]: WeightSpec((self.nh * self.dim, self.rank)),
+             n["uv"]: WeightSpec((self.nh * self.vdim, self.rank)),
+             n["o"]: WeightSpec((H, self.nh * self.vdim))}
+        if self.gated:
+            m[n["gate"]] = WeightSpec((self.nh, H))
+        return m
+
+    def load(self, get):
+        n = self.names
+        q, dkv = get(n["q"]), get(n["dkv"])
+        w = torch.zeros(self.width1, self.hidden, dtype=q.dtype, device=q.device)
+        w[:self.nh * self.dim] = q
+        w[self.col_c:self.col_c + self.rank] = dkv
+        if self.gated:
+            w[self.col_g:self.col_g + self.nh] = get(n["gate"])
+        self.w_in = w.contiguous()
+        self.w_norm = get(n["dkv_norm"]).to(torch.float32).contiguous()
+        # [heads, rank, dim]: the transpose of each head's key expansion, so that the query goes
+        # to the latent's space with the same grouped product that brings the result back
+        self.w_uk_t = get(n["uk"]).view(self.nh, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = get(n["uv"]).view(self.nh, self.vdim, self.rank).contiguous()
+        self.w_o = get(n["o"]).contiguous()
+
+    def forward(self, x, batch, cache, writes_cache=True):
+        T, ws = x.shape[0], self.ctx.workspace
+        kc, vc, group = cache
+        nh, R, Rp = self.nh, self.rank, self.rank_p
+        proj = ws.get("lat_proj", T, self.width1)
+        linear(x, self.w_in, proj)
+        if writes_cache:
+            ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, batch.slot_mapping[group], kc)
+        q = ws.get("lat_q", T, nh * Rp)
+        ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.dim, o_group_cols=Rp,
+                         n_padded=Rp, rows=T)
+        o = ws.get("lat_o", T, nh * Rp)
+        bt = batch.block_tables[group]
+        ps = self.ctx.page_size
+        if batch.num_portions:
+            if TILES_GENERAL not in batch.tiles:
+                raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
+                                   "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
+            t16, t64, t128 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA), batch.tiles.get(TILES_TC)
+            fast = self._fast()
+            if not fast:
+                t64 = t128 = None
+            ops.attn_prefill(q, nh * Rp, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                             t16.seq, t16.q0, t16.count, o, nh, 1, Rp, ps, 0, self.scale,
+                             t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
+                             allow_mma=t64 is not None,
+                             tile128_seq=t128.seq if t128 else None, tile128_q0=t128.q0 if t128 else None,
+                             num_tiles128=t128.count if t128 else 0, allow_tc=t128 is not None)
+        if batch.num_decode:
+            n = batch.num_decode
+            facts = getattr(batch, "facts", None)
+            longest = facts.max_context if facts is not None else max(s + l for s, l in zip(batch.q_starts, batch.q_lens))
+            splits = self._splits(n, longest)
+            ops.attn_decode(q, nh * Rp, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                            batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * nh * splits * Rp),
+                            ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, 1, Rp, ps, 0, self.scale,
+                            allow_mma=self._fast())
+        a = ws.get("attn_out", T, nh * self.vdim)
+        ops.grouped_gemm(o, self.w_uv, a, self.vdim, R, nh, a_group_cols=Rp, o_group_cols=self.vdim, rows=T,
+                         gate=proj if self.gated else None, gate_col0=self.col_g)
+        return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
+
+
+register_mixer("latent_attention", LatentAttention)

@@ -15,6 +15,7 @@ import torch
 from ..config import read_config_json, resolve_architecture
 from ..csrc import ops
 from ..weights import WeightSpec
+from .block import ResidualRows
 from .context import BuildContext
 from .linear import linear
 from .registry import build_block, build_feed_forward, build_mixer, build_norm, build_position
@@ -22,19 +23,34 @@ from .spec import ModelSpec
 
 
 def _prefixed(prefix: str, weights: Dict[str, WeightSpec], single_name: str = "") -> Dict[str, WeightSpec]:
-    return {(single_name if local == "" else prefix + local): spec for local, spec in weights.items()}
+    """Checkpoint names of a part's tensors.  A mixer or feed-forward: prefix + local name.  A norm
+    (``single_name`` given): its one tensor "" has that name, any further tensor (a bias ".b") that
+    name with the local name appended."""
+    if single_name:
+        return {single_name + local: spec for local, spec in weights.items()}
+    return {prefix + local: spec for local, spec in weights.items()}
 
 
-def spec_manifest(spec: ModelSpec, parts=None, embed_position=None) -> Dict[str, WeightSpec]:
+def spec_manifest(spec: ModelSpec, parts=None, embed_position=None, blocks=None, final_norm=None) -> Dict[str, WeightSpec]:
     """Checkpoint tensors the model expects.  ``parts`` = per layer
-    (mixer, feed_forward, mixer_norm, ffn_norm) if already built."""
+    (mixer, feed_forward, mixer_norm, ffn_norm) if already built; ``blocks`` = the layers' blocks
+    (one that has tensors of its own offers ``weights()`` and ``load(get)``)."""
     m: Dict[str, WeightSpec] = {spec.embed_name: WeightSpec((spec.vocab_size, spec.hidden_size))}
     for ls, (mixer, ff, n1, n2) in zip(spec.layers, parts):
         m.update(_prefixed(ls.mixer_prefix, mixer.weights()))
-        m.update(_prefixed(ls.ffn_prefix, ff.weights()))
-        m.update(_prefixed("", n1.weights(), ls.mixer_norm_name))
-        m.update(_prefixed("", n2.weights(), ls.ffn_norm_name))
-    m[spec.final_norm_name] = WeightSpec((spec.hidden_size,))
+        if ff is not None:
+            m.update(_prefixed(ls.ffn_prefix, ff.weights()))
+        if n1 is not None:
+            m.update(_prefixed("", n1.weights(), ls.mixer_norm_name))
+        if n2 is not None:
+            m.update(_prefixed("", n2.weights(), ls.ffn_norm_name))
+    for ls, block in zip(spec.layers, blocks or ()):
+        if hasattr(block, "weights"):
+            m.update(_prefixed(ls.block_prefix, block.weights()))
+    if final_norm is not None:
+        m.update(_prefixed("", final_norm.weights(), spec.final_norm_name))
+    else:
+        m[spec.final_norm_name] = WeightSpec((spec.hidden_size,))
     if embed_position is not None:
         m.update(_prefixed(spec.embed_position_prefix, embed_position.weights()))
     m[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), optional=spec.tie_embeddings)
@@ -48,8 +64,10 @@ class DecoderModel:
         self.blocks = []
         for ls in spec.layers:
             mixer = build_mixer(ls.mixer, ctx)
-            ff = build_feed_forward(ls.feed_forward, ctx)
-            n1, n2 = build_norm(ls.mixer_norm, ctx), build_norm(ls.ffn_norm, ctx)
+            # a layer may have no feed-forward (and then no norm for it)
+            ff = build_feed_forward(ls.feed_forward, ctx) if ls.feed_forward is not None else None
+            n1 = build_norm(ls.mixer_norm, ctx)
+            n2 = build_norm(ls.ffn_norm, ctx) if ls.ffn_norm is not None else None
             self.parts.append((mixer, ff, n1, n2))
             self.blocks.append(build_block(ls, mixer, ff, n1, n2, ctx))
         self.final_norm = build_norm(spec.final_norm, ctx)
@@ -64,7 +82,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ weights
     def manifest(self) -> Dict[str, WeightSpec]:
-        return spec_manifest(self.spec, self.parts, self.embed_position)
+        return spec_manifest(self.spec, self.parts, self.embed_position, self.blocks, self.final_norm)
 
     def load(self, get: Callable[[str], torch.Tensor]) -> None:
         """Bind weights: ``get(name)`` delivers a checkpoint tensor on the device."""
@@ -72,10 +90,16 @@ class DecoderModel:
         self.embed = get(s.embed_name).contiguous()
         for ls, (mixer, ff, n1, n2) in zip(s.layers, self.parts):
             mixer.load(lambda local, p=ls.mixer_prefix: get(p + local))
-            ff.load(lambda local, p=ls.ffn_prefix: get(p + local))
-            n1.load(lambda local, n=ls.mixer_norm_name: get(n))
-            n2.load(lambda local, n=ls.ffn_norm_name: get(n))
-        self.final_norm.load(lambda local: get(s.final_norm_name))
+            if ff is not None:
+                ff.load(lambda local, p=ls.ffn_prefix: get(p + local))
+            if n1 is not None:
+                n1.load(lambda local, n=ls.mixer_norm_name: get(n + local))
+            if n2 is not None:
+                n2.load(lambda local, n=ls.ffn_norm_name: get(n + local))
+        for ls, block in zip(s.layers, self.blocks):
+            if hasattr(block, "load"):
+                block.load(lambda local, p=ls.block_prefix: get(p + local))
+        self.final_norm.load(lambda local: get(s.final_norm_name + local))
         if self.embed_position is not None:
             self.embed_position.load(lambda local, p=s.embed_position_prefix: get(p + local))
         head = None if s.tie_embeddings else get(s.head_name)
@@ -88,12 +112,20 @@ class DecoderModel:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-        add(self.embed), add(self.head), add(self.final_norm.weight)
-        for mixer, ff, n1, n2 in self.parts:
-            for part in (mixer, ff, n1, n2):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.is_cuda:
-                        add(v)
+        add(self.embed), add(self.head)
+        def add_part(part, depth=0):
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.is_cuda:
+                    add(v)
+                elif depth < 2 and hasattr(v, "weights") and hasattr(v, "load"):     # a part inside a part
+                    add_part(v, depth + 1)
+        add_part(self.final_norm)
+        for parts, block in zip(self.parts, self.blocks):
+            for part in parts:
+                if part is not None:
+                    add_part(part)
+            for name in ("scale1", "scale2"):
+                add(getattr(block, name, None))
         return total
 
     # ------------------------------------------------------------------ cache
@@ -122,7 +154,7 @@ class DecoderModel:
         tags = set()
         for parts in self.parts:
             for part in parts:
-                f = getattr(part, "step_tags", None)
+                f = getattr(part, "step_tags", None) if part is not None else None
                 if f is not None:
                     tags.update(f(facts))
         return tuple(sorted(tags))
@@ -153,6 +185,8 @@ class DecoderModel:
         if R == 0:
             return logits
         h = ws.get("head_in", R, H)
+        if isinstance(delta, ResidualRows):
+            delta = None                       # the last block has added everything to the residual itself
         self.final_norm.add_norm(resid, delta, h, rows=batch.logit_rows, write_back=False)
         linear(h, self.head, logits)
         return logits

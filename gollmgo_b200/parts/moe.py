@@ -1,0 +1,106 @@
+"""A mixture of experts as a feed-forward: a router picks ``top`` of ``experts`` small SiLU-gated
+feed-forwards per token, their results are summed with the router's weights, and an optional
+shared expert (any registered feed-forward) runs for every token and is added.
+
+Router: logits = x Wr^T + b in float32; the ``top`` largest are chosen and weighted by the
+softmax over the chosen logits alone.  Everything happens on the device (csrc/moe.cu): the
+(token, choice) pairs are sorted by expert there, two grouped products (csrc/grouped_gemm.cu) run
+every expert over its own rows (first product with the gate's activation in its epilogue), and a
+last kernel sums each token's results in float32.  No count ever reaches the host, so a step of
+decoded tokens is captured like any other.
+
+params: hidden_size, intermediate_size, experts, top, router_bias (bool), shared (a feed-forward
+PartSpec or None), names: dict with "router", "router_bias", "expert" (a format string with
+{e}), "gate", "up", "down", "shared" (prefix of the shared expert's tensors).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights import WeightSpec
+from .registry import build_feed_forward, register_feed_forward
+
+DEFAULT_NAMES = {"router": "router", "router_bias": "router.b", "expert": "e{e}.", "gate": "gate",
+                 "up": "up", "down": "down", "shared": "shared."}
+
+
+class MixtureOfExperts:
+    def __init__(self, spec, ctx):
+        self.ctx = ctx
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        if not (0 < self.top <= self.experts):
+            raise ValueError(f"{self.top} choices of {self.experts} experts")
+        if self.experts > ops.MOE_MAX_EXPERTS or self.top > ops.MOE_MAX_TOP:
+            raise ValueError(f"the routing kernels take at most {ops.MOE_MAX_EXPERTS} experts and "
+                             f"{ops.MOE_MAX_TOP} choices a token")
+        self.router_bias = bool(spec.get("router_bias", True))
+        self.names = {**DEFAULT_NAMES, **(spec.get("names") or {})}
+        shared = spec.get("shared")
+        self.shared = build_feed_forward(shared, ctx) if shared is not None else None
+        ws, T = ctx.workspace, ctx.max_tokens
+        n = T * self.top
+        ws.reserve("moe_idx", n, torch.int32)
+        ws.reserve("moe_wgt", n, torch.float32)
+        ws.reserve("moe_order", n, torch.int32)
+        ws.reserve("moe_place", n, torch.int32)
+        ws.reserve("moe_offsets", self.experts + 1, torch.int32)
+        ws.reserve("moe_act", n * self.inter, ctx.act_dtype)
+        ws.reserve("moe_rows", n * self.hidden, ctx.act_dtype)
+        ws.reserve("moe_out", T * self.hidden, ctx.act_dtype)
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def _expert(self, e, which):
+        return self.names["expert"].format(e=e) + self.names[which]
+
+    def weights(self):
+        m = {self.names["router"]: WeightSpec((self.experts, self.hidden))}
+        if self.router_bias:
+            m[self.names["router_bias"]] = WeightSpec((self.experts,))
+        for e in range(self.experts):
+            m[self._expert(e, "gate")] = WeightSpec((self.inter, self.hidden))
+            m[self._expert(e, "up")] = WeightSpec((self.inter, self.hidden))
+            m[self._expert(e, "down")] = WeightSpec((self.hidden, self.inter))
+        if self.shared is not None:
+            m.update({self.names["shared"] + k: v for k, v in self.shared.weights().items()})
+        return m
+
+    def load(self, get):
+        self.w_router = get(self.names["router"]).contiguous()
+        self.b_router = get(self.names["router_bias"]).to(torch.float32).contiguous() if self.router_bias else None
+        # [experts, 2 * inter, hidden]: an expert's gate rows, then its up rows
+        self.w_gate_up = torch.stack([torch.cat([get(self._expert(e, "gate")), get(self._expert(e, "up"))], dim=0)
+                                      for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([get(self._expert(e, "down")) for e in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.load(lambda local: get(self.names["shared"] + local))
+
+    def route(self, x):
+        """(choices [T, top] int32, weights [T, top] float32) of the rows x."""
+        T, ws = x.shape[0], self.ctx.workspace
+        idx, wgt = ws.get("moe_idx", T, self.top), ws.get("moe_wgt", T, self.top)
+        ops.moe_route(x, self.w_router, self.b_router, self.top, idx, wgt)
+        return idx, wgt
+
+    def forward(self, x, batch):
+        T, ws = x.shape[0], self.ctx.workspace
+        n, E = T * self.top, self.experts
+        idx, wgt = self.route(x)
+        order, place = ws.get("moe_order", 1, n), ws.get("moe_place", 1, n)
+        offsets = ws.get("moe_offsets", 1, E + 1)
+        ops.moe_align(idx, n, E, offsets, order, place)
+        a = ws.get("moe_act", n, self.inter)
+        ops.grouped_gemm(x, self.w_gate_up, a, self.inter, self.hidden, E, offsets=offsets, row_index=order,
+                         row_div=self.top, rows=n, gated=True)
+        y = ws.get("moe_rows", n, self.hidden)
+        ops.grouped_gemm(a, self.w_down, y, self.hidden, self.inter, E, offsets=offsets, rows=n)
+        shared = self.shared.forward(x, batch) if self.shared is not None else None
+        out = ws.get("moe_out", T, self.hidden)
+        ops.moe_combine(y, place, wgt, shared, out, self.top)
+        return out
+
+
+register_feed_forward("moe", MixtureOfExperts)

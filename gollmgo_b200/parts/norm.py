@@ -1,4 +1,5 @@
-"""RMSNorm, fused with the residual add that precedes it.
+"""RMSNorm and LayerNorm, fused with the residual add that precedes them, or (norm_scale_add)
+with the scaling and the residual add that follow them.
 
 y = x * rsqrt(mean(x^2) + eps) * w in float32 (kernels/gollmgo_ops.cu:593-629);
 eps comes from config.json (the reference passes the literal 1e-5:
@@ -38,4 +39,37 @@ class RMSNorm:
         return out
 
 
+    def norm_scale_add(self, resid, y, scale, copy):
+        """resid += scale * norm(y); copy = resid in the activation type (a block that norms what a
+        sublayer returns: parts/block.py)."""
+        ops.norm_scale_add(resid, y, self.weight, None, scale, copy, self.eps, layer=False)
+
+
+class LayerNorm:
+    """(x - mean) / sqrt(variance + eps) * weight + bias, the variance the mean of the squared
+    deviations; statistics in float32.  params: size, eps.  Its tensors: "" (weight), ".b" (bias)."""
+
+    def __init__(self, spec, ctx):
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.ctx = ctx
+        self.weight = None
+        self.bias = None
+
+    def weights(self):
+        return {"": WeightSpec((self.size,)), ".b": WeightSpec((self.size,))}
+
+    def load(self, get):
+        self.weight = get("").to(torch.float32).contiguous()
+        self.bias = get(".b").to(torch.float32).contiguous()
+
+    def add_norm(self, resid, delta, out, rows=None, write_back=True):
+        ops.add_norm(resid, delta, self.weight, self.bias, out, self.eps, rows, write_back, layer=True)
+        return out
+
+    def norm_scale_add(self, resid, y, scale, copy):
+        ops.norm_scale_add(resid, y, self.weight, self.bias, scale, copy, self.eps, layer=True)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

@@ -34,15 +34,18 @@ class PartSpec:
 class LayerSpec:
     block: PartSpec                    # arrangement, e.g. "pre_norm"
     mixer: PartSpec                    # e.g. "attention"
-    feed_forward: PartSpec             # e.g. "gated_mlp"
-    mixer_norm: PartSpec               # norm before the mixer
-    ffn_norm: PartSpec                 # norm before the feed-forward
+    feed_forward: Optional[PartSpec]   # e.g. "gated_mlp"; None: the layer has no feed-forward
+    mixer_norm: PartSpec               # norm before (or, in a post-norm block, after) the mixer
+    ffn_norm: Optional[PartSpec]       # norm before (or, in a post-norm block, after) the feed-forward
     # checkpoint names: prefix of the mixer's and feed-forward's tensors, full
     # names of the two norm weights
     mixer_prefix: str = ""
     ffn_prefix: str = ""
     mixer_norm_name: str = ""
     ffn_norm_name: str = ""
+    # prefix of the tensors that belong to the block itself (per-channel scales of its two
+    # branches, say); a block without tensors ignores it
+    block_prefix: str = ""
 
 
 @dataclass(frozen=True)
@@ -72,6 +75,9 @@ class ModelSpec:
     # mixers do all the position encoding there is (rotary: inside attention)
     embed_position: Optional[PartSpec] = None
     embed_position_prefix: str = ""
+    # name patterns (fnmatch) of checkpoint tensors that this model does not use and a
+    # checkpoint may still hold
+    ignorable_tensors: Tuple[str, ...] = ()
 
     @property
     def num_cache_entries(self) -> int:

@@ -80,12 +80,13 @@ def check_manifest(manifest: Dict[str, WeightSpec], found: Dict[str, Tuple[Tuple
 
 
 def checkpoint_source(model_dir: str, manifest: Dict[str, WeightSpec], engine_dtype: torch.dtype,
-                      device) -> Callable[[str], torch.Tensor]:
+                      device, ignorable: Iterable[str] = ()) -> Callable[[str], torch.Tensor]:
     """Check the checkpoint in ``model_dir`` against ``manifest``; return ``get(name)``
     that delivers each tensor on ``device`` in its storage dtype (None if optional
-    and absent)."""
+    and absent).  ``ignorable``: further name patterns of tensors the model does not use."""
     index = open_model_files(model_dir)
-    check_manifest(manifest, {n: (e.shape, e.dtype) for n, (_, e) in index.items()})
+    check_manifest(manifest, {n: (e.shape, e.dtype) for n, (_, e) in index.items()},
+                   tuple(IGNORABLE) + tuple(ignorable))
 
     def get(name: str):
         if name not in index:
