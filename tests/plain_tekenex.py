@@ -57,19 +57,32 @@ def route(h, p, pre, top):
     return idx, torch.softmax(val, dim=-1)
 
 
-def moe_ff(h, p, pre, experts, top, shared):
+def route_gap(h, p, pre, top):
+    """Per token, how far the last chosen logit lies above the first one left out, as a share of
+    the largest logit's size: a small gap is a choice that rounding can turn."""
+    z = h @ p[pre + "router"].T + p[pre + "router.b"]
+    if top >= z.shape[-1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    val = torch.topk(z, top + 1, dim=-1).values
+    return (val[:, top - 1] - val[:, top]) / z.abs().max(-1).values
+
+
+def moe_ff(h, p, pre, experts, top, shared, gaps=None):
     idx, w = route(h, p, pre, top)
+    if gaps is not None:
+        gaps.append(route_gap(h, p, pre, top))
     out = torch.zeros(h.shape[0], p[pre + "e0.down"].shape[0], dtype=h.dtype)
-    for t in range(h.shape[0]):
+    for e in range(experts):
         for j in range(top):
-            e = int(idx[t, j])
-            out[t] += w[t, j] * gated_expert(h[t:t + 1], p, f"{pre}e{e}.")[0]
+            rows = (idx[:, j] == e).nonzero()[:, 0]             # the tokens whose j-th choice is expert e
+            if rows.numel():
+                out[rows] += w[rows, j, None] * gated_expert(h[rows], p, f"{pre}e{e}.")
     if shared:
         out = out + gated_expert(h, p, pre + "shared.")
     return out
 
 
-def layer(x, p, i, lc, eps):
+def layer(x, p, i, lc, eps, gaps=None):
     pre = f"l{i}."
     m = lc["mixer"]
     if lc["type"] != "latent_attention":
@@ -82,20 +95,20 @@ def layer(x, p, i, lc, eps):
     if f["kind"] == "dense":
         y = dense_ff(x, p, pre + "mlp.")
     elif f["kind"] == "moe":
-        y = moe_ff(x, p, pre + "mlp.", f["router"]["experts"], f["router"]["top"], f.get("shared"))
+        y = moe_ff(x, p, pre + "mlp.", f["router"]["experts"], f["router"]["top"], f.get("shared"), gaps)
     else:
         raise ValueError(f["kind"])
     return x + p[pre + "ls2"] * layer_norm(y, p[pre + "norm2"], p[pre + "norm2.b"], eps)
 
 
-def forward(config, p, tokens, dtype=torch.float64, trace=None):
+def forward(config, p, tokens, dtype=torch.float64, trace=None, gaps=None):
     """Logits [n, vocab] of one sequence.  ``trace``: a list that receives the residual stream
-    after every layer."""
+    after every layer; ``gaps``: a list that receives every routed layer's route_gap."""
     p = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in p.items()}
     eps = config["norm"]["eps"]
     x = p["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for i, lc in enumerate(config["layers"]):
-        x = layer(x, p, i, lc, eps)
+        x = layer(x, p, i, lc, eps, gaps)
         if trace is not None:
             trace.append(x.clone())
     return layer_norm(x, p["final.norm"], p["final.norm.b"], eps) @ p["embed"].T
