@@ -152,6 +152,80 @@ def reference_arm(args) -> int:
     return 0
 
 
+def design_bench(args) -> int:
+    """--design tekenex: prefill and decode throughput of Tekenex at sizes that resemble a real
+    model's layers (random weights), each beside the closest model this engine had before, a Llama
+    decoder of equal width, depth, heads, head size and vocabulary with one kv head (its cache
+    rows are as wide as the latent's).  One JSON line; the default workload is untouched."""
+    import torch
+    from gollmgo_b200 import Engine, EngineConfig
+    from gollmgo_b200.csrc import ops
+    from gollmgo_b200.engine.batch import StepEntry
+    W, K = max(args.warmup, 3), max(min(args.steps, 64), 1)
+    pairs = [("tekenex_w2048", "llama_mqa_w2048"), ("tekenex_w4096", "llama_mqa_w4096")]
+    batches = (1, 8, 64)
+    rows = {}
+    for shape in [s for pair in pairs for s in pair]:
+        with open(os.path.join(ROOT, "gollmgo_b200", "bench_shapes", shape + ".json")) as f:
+            cfg = json.load(f)
+        per_seq = CONTEXT + 2 * (K + W) + 64
+        ecfg = EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=(max(batches) + 1) * (-(-per_seq // PAGE)) + 256,
+                            max_batch_size=max(batches), max_token_budget=PREFILL_TOKENS + max(batches),
+                            prefill_chunk_size=PREFILL_TOKENS, max_model_len=per_seq + PREFILL_TOKENS, max_queue_depth=0)
+        eng = Engine(config=cfg, weights_seed=0, engine_config=ecfg)
+        runner, dev = eng.runner, eng.runner.device
+        V = runner.spec.vocab_size
+        gen = torch.Generator().manual_seed(1)
+        rp = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+
+        def timed(fn, n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            a.record()
+            for i in range(n):
+                fn(i)
+            b.record()
+            torch.cuda.synchronize(dev)
+            return a.elapsed_time(b) / n
+        prompts = [rp(PREFILL_TOKENS) for _ in range(4)]
+
+        def prefill_once(i):
+            rid = f"pf{i}-{time.monotonic_ns()}"
+            runner.step([StepEntry(rid, prompts[i % 4], [PREFILL_TOKENS - 1])])
+            runner.release(rid)
+        for i in range(3):
+            prefill_once(i)
+        pf_ms = timed(prefill_once, 4)
+        row = {"weights_GB": round(runner.model.weight_bytes() / 1e9, 3), "prefill_2048_ms": round(pf_ms, 3),
+               "prefill_tokens_per_s": round(PREFILL_TOKENS / pf_ms * 1e3, 1)}
+        out = torch.empty(max(batches), dtype=torch.int32, device=dev)
+        for b in batches:
+            ids = [f"d{b}-{j}" for j in range(b)]
+            for rid in ids:
+                runner.step([StepEntry(rid, rp(CONTEXT), [])])
+            toks = rp(b)
+
+            def one(i):
+                ops.argmax(runner.step([StepEntry(rid, [toks[j]], [0]) for j, rid in enumerate(ids)]), out[:b])
+            for i in range(W):
+                one(i)
+            l0 = ops.launches
+            ms = timed(one, K)
+            row[f"decode_b{b}_ms"] = round(ms, 4)
+            row[f"decode_b{b}_tokens_per_s"] = round(b / ms * 1e3, 1)
+            row[f"decode_b{b}_launches_per_step"] = (ops.launches - l0) // K
+            for rid in ids:
+                runner.release(rid)
+        rows[shape] = row
+        eng.stop()
+        del eng, runner
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "Tekenex beside the closest model at equal size: prefill of 2048 tokens and decode at context 2048",
+                      "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+                      "n_gpus": 1, "steps": K, "warmup": W, "pairs": pairs, "shapes": rows, "peaks": peaks()}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,9 +235,13 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--design", default=None, choices=["tekenex"],
+                    help="instead of the default workload: that design at a few sizes beside the closest model at equal size")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_bench(args)
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
         return 2

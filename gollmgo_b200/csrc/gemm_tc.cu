@@ -41,7 +41,7 @@ template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ out, int M, int N, int K, int tiles_m, int num_tiles,
-               int* __restrict__ status, int withhold_loads) {
+               int* __restrict__ status, int withhold_loads, const int* __restrict__ tile_group, int group_rows) {
   constexpr int BN = 256;
   constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
@@ -80,6 +80,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * n_out_tile;
+      int w0 = 0;                               // first row of this row block's group in W (grouped product)
+      if (tile_group) {
+        const int g = tile_group[t % tiles_m];
+        if (g < 0) continue;                    // a row block no group owns: nothing to compute
+        w0 = g * group_rows;
+      }
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % TC_STAGES;
         const unsigned phase = (it / TC_STAGES) & 1;
@@ -89,10 +95,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
         tma_load_2d(a_dst, &map_x, kb * TC_BK, m0, full0 + 8 * s);
         if (MODE == TC_OUT_SILU) {
-          tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                      // 128 gate rows
-          tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, N + n0, full0 + 8 * s);    // 128 up rows
+          tma_load_2d(b_dst, &map_w, kb * TC_BK, w0 + n0, full0 + 8 * s);                      // 128 gate rows
+          tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, w0 + N + n0, full0 + 8 * s);    // 128 up rows
         } else {
-          tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+          tma_load_2d(b_dst, &map_w, kb * TC_BK, w0 + n0, full0 + 8 * s);
         }
         issued = it + 1;
       }
@@ -108,7 +114,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
     bool ok = true;
     int it = 0, local = 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      if (tile_group && tile_group[t % tiles_m] < 0) continue;
       const int buf = local & 1;
       // the epilogue must have drained this buffer (two tiles ago)
       if (!mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) & 1) ^ 1)) { atomicExch(status, TC_ERR_ACC_WAIT); atomicExch(&abort_s, 1); ok = false; break; }
@@ -128,12 +135,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
       }
       tc_commit(acc_full0 + 8 * buf);                 // this tile's accumulator is complete (also on abort)
+      ++local;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue: warp w reads tensor-memory lanes 32*(w%4) .. +32
     const int quarter = warp & 3;
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      if (tile_group && tile_group[t % tiles_m] < 0) continue;
       const int buf = local & 1;
       const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * n_out_tile;
       const int row = m0 + quarter * 32 + lane;
@@ -174,6 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+      ++local;
     }
   }
   tc_fence_before();
@@ -217,11 +227,25 @@ int gg_make_map_2d(CUtensorMap* map, const void* ptr, int rows, int cols, long l
 // rows), out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T).  status: one int in device memory,
 // left untouched unless a wait inside the kernel ran out (then non-zero).
 static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
-                          int mode, int* status, int withhold_loads, cudaStream_t stream);
+                          int mode, int* status, int withhold_loads, cudaStream_t stream,
+                          const int* tile_group = nullptr, int groups = 1);
 
 extern "C" int gg_gemm_tc(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
                           int mode, int* status, cudaStream_t stream) {
   return gemm_tc_launch(x, ldx, W, out, M, N, K, mode, status, 0, stream);
+}
+
+// The grouped product: W holds `groups` matrices one after the other ([groups, N, K], or
+// [groups, 2N, K] gated), and every block of 128 rows of x belongs to one of them:
+// tile_group[i] (device memory, written by a kernel earlier in the stream) is the group of rows
+// 128 i .. 128 i + 127, or < 0 for a block that belongs to none and is skipped.  The rows of a
+// group therefore start at a multiple of 128 (the caller pads).  M = rows of x and out.
+extern "C" int gg_gemm_tc_grouped(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
+                                  int mode, const int* tile_group, int groups, int* status, cudaStream_t stream) {
+  GG_REQUIRE(tile_group != nullptr && groups > 0, "gemm_tc_grouped: no groups given");
+  GG_REQUIRE(M % TC_BM == 0, "gemm_tc_grouped: %d rows are no multiple of %d", M, TC_BM);
+  GG_REQUIRE(mode == TC_OUT_BF16 || mode == TC_OUT_SILU, "gemm_tc_grouped: mode %d", mode);
+  return gemm_tc_launch(x, ldx, W, out, M, N, K, mode, status, 0, stream, tile_group, groups);
 }
 
 // Self-test of the bounded waits: the same launch, but the loads are withheld, so no barrier a
@@ -233,7 +257,8 @@ extern "C" int gg_gemm_tc_withheld(const void* x, long long ldx, const void* W, 
 }
 
 static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
-                          int mode, int* status, int withhold_loads, cudaStream_t stream) {
+                          int mode, int* status, int withhold_loads, cudaStream_t stream,
+                          const int* tile_group, int groups) {
   GG_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   GG_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K=%d and the row stride %lld of x must be multiples of 8", K, ldx);
   GG_REQUIRE(((size_t)x % 16) == 0 && ((size_t)W % 16) == 0, "gemm_tc: x and W must be 16-byte aligned");
@@ -246,7 +271,8 @@ static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out
   int rc = gg_make_map_2d(&map_x, x, M, K, ldx, TC_BM);
   if (rc) return rc;
   const int w_rows = mode == TC_OUT_SILU ? 2 * N : N;
-  rc = gg_make_map_2d(&map_w, W, w_rows, K, K, mode == TC_OUT_SILU ? 128 : 256);
+  GG_REQUIRE((long long)w_rows * groups < (1ll << 31), "gemm_tc: W has too many rows");
+  rc = gg_make_map_2d(&map_w, W, w_rows * groups, K, K, mode == TC_OUT_SILU ? 128 : 256);
   if (rc) return rc;
   const int n_tile = mode == TC_OUT_SILU ? 128 : 256;
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + n_tile - 1) / n_tile;
@@ -271,7 +297,7 @@ static int gemm_tc_launch(const void* x, long long ldx, const void* W, void* out
       if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));            \
       set = true;                                                                                         \
     }                                                                                                     \
-    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, tiles_m, num_tiles, status, withhold_loads); \
+    e = gg_launch(gemm_tc_kernel<MODE>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, out, M, N, K, tiles_m, num_tiles, status, withhold_loads, tile_group, w_rows); \
   } while (0)
   if (mode == TC_OUT_BF16) TC_LAUNCH(TC_OUT_BF16);
   else if (mode == TC_OUT_F32) TC_LAUNCH(TC_OUT_F32);

@@ -15,7 +15,10 @@
 // whose tile lies past its group's rows returns.  A row's result depends on that row and on W_g
 // alone (fixed order over K), so it is the same wherever the row lands in its group's list.
 // bfloat16: tensor cores through wmma 16x16x16 with float32 accumulators; float32: FMA.  Tiles
-// of 32 rows x 64 columns, K in steps of 32 through shared memory, any N and K.
+// of 32 rows x 64 columns, K in steps through shared memory, any N and K.  This is the kernel for
+// few rows per group (decoded tokens, heads of short steps) and for float32; long prompt steps
+// of a mixture of experts in bfloat16 go through the tcgen05 product instead (gemm_tc.cu,
+// gg_gemm_tc_grouped).
 #include <mma.h>
 
 #include <type_traits>
@@ -24,8 +27,6 @@
 
 #define GGM_BM 32
 #define GGM_BN 64
-#define GGM_BK 32
-#define GGM_LD (GGM_BK + 8)
 #define GGM_LDC (GGM_BN + 8)
 #define GGM_THREADS 256
 
@@ -43,12 +44,26 @@ template <typename TA> struct GgmZero;
 template <> struct GgmZero<float> { static __device__ __forceinline__ float v() { return 0.f; } };
 template <> struct GgmZero<__nv_bfloat16> { static __device__ __forceinline__ __nv_bfloat16 v() { return __float2bfloat16_rn(0.f); } };
 
-template <typename TA, bool GATED>
+// K is walked in steps of BK (128 for bfloat16, 32 for float32).  VEC: every row of A and W
+// starts on a 16-byte boundary and K is a multiple of the 16-byte chunk, so tiles are fetched
+// in chunks of 16 bytes, and the chunks of the next step are asked for (into registers) before
+// the products of this one, which hides most of a trip to memory when a group has only a few
+// rows and the kernel streams its weights (decoded tokens).
+template <typename TA, bool GATED, int BK, bool VEC>
 __global__ void __launch_bounds__(GGM_THREADS) grouped_gemm_kernel(GroupedArgs a) {
-  __shared__ __align__(32) TA As[GGM_BM * GGM_LD];
-  __shared__ __align__(32) TA Bs[GATED ? 2 : 1][GGM_BN * GGM_LD];
-  __shared__ __align__(32) float Cs[GATED ? 2 : 1][GGM_BM * GGM_LDC];
+  constexpr int LD = BK + 8;
+  constexpr int NB = GATED ? 2 : 1;
+  constexpr int VPT = 16 / (int)sizeof(TA);                     // values in a 16-byte chunk
+  constexpr int CPR = BK / VPT;                                 // chunks in a tile row
+  constexpr int A_CH = GGM_BM * CPR / GGM_THREADS, B_CH = GGM_BN * CPR / GGM_THREADS;
+  static_assert(GGM_BM * CPR % GGM_THREADS == 0 && GGM_BN * CPR % GGM_THREADS == 0, "tile chunks must divide over the threads");
+  constexpr int AB_BYTES = (GGM_BM + NB * GGM_BN) * LD * (int)sizeof(TA);
+  constexpr int C_BYTES = NB * GGM_BM * GGM_LDC * (int)sizeof(float);
+  __shared__ __align__(32) unsigned char raw[AB_BYTES > C_BYTES ? AB_BYTES : C_BYTES];
   __shared__ int arow_s[GGM_BM];
+  TA* As = reinterpret_cast<TA*>(raw);
+  TA* Bs = As + GGM_BM * LD;                                    // [NB][GGM_BN * LD]
+  float* Cs = reinterpret_cast<float*>(raw);                    // [NB][GGM_BM * GGM_LDC], over the tiles once they are used up
   pdl_trigger();
   pdl_wait();
   const int tid = threadIdx.x;
@@ -72,7 +87,7 @@ __global__ void __launch_bounds__(GGM_THREADS) grouped_gemm_kernel(GroupedArgs a
   __syncthreads();
   const int N = a.N, K = a.K;
   const TA* A = (const TA*)a.A + (size_t)g * a.a_group_cols;
-  const TA* W = (const TA*)a.W + (size_t)g * (GATED ? 2 : 1) * N * K;
+  const TA* W = (const TA*)a.W + (size_t)g * NB * N * K;
   const TA zero = GgmZero<TA>::v();
 
   constexpr bool TC = !std::is_same<TA, float>::value;
@@ -89,55 +104,91 @@ __global__ void __launch_bounds__(GGM_THREADS) grouped_gemm_kernel(GroupedArgs a
     for (int j = 0; j < 8; ++j) { f0[j] = 0.f; f1[j] = 0.f; }
   }
 
-  for (int k0 = 0; k0 < K; k0 += GGM_BK) {
-    for (int e = tid; e < GGM_BM * GGM_BK; e += GGM_THREADS) {
-      const int r = e / GGM_BK, c = e - r * GGM_BK;
-      const int row = arow_s[r], k = k0 + c;
-      As[r * GGM_LD + c] = (row >= 0 && k < K) ? A[(size_t)row * a.lda + k] : zero;
+  uint4 ra[A_CH], rb[NB][B_CH];
+  auto fetch = [&](int k0) {                               // VEC: this step's chunks into registers
+#pragma unroll
+    for (int u = 0; u < A_CH; ++u) {
+      const int e = tid + u * GGM_THREADS, r = e / CPR, k = k0 + (e - r * CPR) * VPT;
+      const int row = arow_s[r];
+      ra[u] = (row >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)row * a.lda + k) : make_uint4(0, 0, 0, 0);
     }
-    for (int e = tid; e < GGM_BN * GGM_BK; e += GGM_THREADS) {
-      const int n = e / GGM_BK, c = e - n * GGM_BK;
-      const int col = n0 + n, k = k0 + c;
-      const bool ok = col < N && k < K;
-      Bs[0][n * GGM_LD + c] = ok ? W[(size_t)col * K + k] : zero;
-      if (GATED) Bs[GATED ? 1 : 0][n * GGM_LD + c] = ok ? W[(size_t)(N + col) * K + k] : zero;
+#pragma unroll
+    for (int u = 0; u < B_CH; ++u) {
+      const int e = tid + u * GGM_THREADS, n = e / CPR, k = k0 + (e - n * CPR) * VPT;
+      const bool ok = n0 + n < N && k < K;
+      rb[0][u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)(n0 + n) * K + k) : make_uint4(0, 0, 0, 0);
+      if (GATED) rb[NB - 1][u] = ok ? *reinterpret_cast<const uint4*>(W + (size_t)(N + n0 + n) * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto stash = [&]() {                                     // VEC: the registers into the shared tiles
+#pragma unroll
+    for (int u = 0; u < A_CH; ++u) {
+      const int e = tid + u * GGM_THREADS, r = e / CPR, c = (e - r * CPR) * VPT;
+      *reinterpret_cast<uint4*>(As + r * LD + c) = ra[u];
+    }
+#pragma unroll
+    for (int u = 0; u < B_CH; ++u) {
+      const int e = tid + u * GGM_THREADS, n = e / CPR, c = (e - n * CPR) * VPT;
+      *reinterpret_cast<uint4*>(Bs + n * LD + c) = rb[0][u];
+      if (GATED) *reinterpret_cast<uint4*>(Bs + (NB - 1) * GGM_BN * LD + n * LD + c) = rb[NB - 1][u];
+    }
+  };
+  if (VEC) fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    if (VEC) {
+      stash();
+    } else {
+      for (int e = tid; e < GGM_BM * BK; e += GGM_THREADS) {
+        const int r = e / BK, c = e - r * BK;
+        const int row = arow_s[r], k = k0 + c;
+        As[r * LD + c] = (row >= 0 && k < K) ? A[(size_t)row * a.lda + k] : zero;
+      }
+      for (int e = tid; e < GGM_BN * BK; e += GGM_THREADS) {
+        const int n = e / BK, c = e - n * BK;
+        const int col = n0 + n, k = k0 + c;
+        const bool ok = col < N && k < K;
+        Bs[n * LD + c] = ok ? W[(size_t)col * K + k] : zero;
+        if (GATED) Bs[(NB - 1) * GGM_BN * LD + n * LD + c] = ok ? W[(size_t)(N + col) * K + k] : zero;
+      }
     }
     __syncthreads();
+    if (VEC && k0 + BK < K) fetch(k0 + BK);
     if constexpr (TC) {
       using namespace nvcuda;
       wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
       wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
 #pragma unroll
-      for (int kk = 0; kk < GGM_BK; kk += 16) {
-        wmma::load_matrix_sync(fa, As + rt * 16 * GGM_LD + kk, GGM_LD);
-        wmma::load_matrix_sync(fb, Bs[0] + ct * 16 * GGM_LD + kk, GGM_LD);
+      for (int kk = 0; kk < BK; kk += 16) {
+        wmma::load_matrix_sync(fa, As + rt * 16 * LD + kk, LD);
+        wmma::load_matrix_sync(fb, Bs + ct * 16 * LD + kk, LD);
         wmma::mma_sync(acc0, fa, fb, acc0);
         if (GATED) {
-          wmma::load_matrix_sync(fb, Bs[GATED ? 1 : 0] + ct * 16 * GGM_LD + kk, GGM_LD);
+          wmma::load_matrix_sync(fb, Bs + (NB - 1) * GGM_BN * LD + ct * 16 * LD + kk, LD);
           wmma::mma_sync(acc1, fa, fb, acc1);
         }
       }
     } else {
 #pragma unroll 8
-      for (int k = 0; k < GGM_BK; ++k) {
-        const float av = As[frow * GGM_LD + k];
+      for (int k = 0; k < BK; ++k) {
+        const float av = As[frow * LD + k];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          f0[j] = fmaf(av, Bs[0][(fcg + 8 * j) * GGM_LD + k], f0[j]);
-          if (GATED) f1[j] = fmaf(av, Bs[GATED ? 1 : 0][(fcg + 8 * j) * GGM_LD + k], f1[j]);
+          f0[j] = fmaf(av, Bs[(fcg + 8 * j) * LD + k], f0[j]);
+          if (GATED) f1[j] = fmaf(av, Bs[(NB - 1) * GGM_BN * LD + (fcg + 8 * j) * LD + k], f1[j]);
         }
       }
     }
     __syncthreads();
   }
+  float* Cs1 = Cs + (NB - 1) * GGM_BM * GGM_LDC;
   if constexpr (TC) {
-    nvcuda::wmma::store_matrix_sync(Cs[0] + rt * 16 * GGM_LDC + ct * 16, acc0, GGM_LDC, nvcuda::wmma::mem_row_major);
-    if (GATED) nvcuda::wmma::store_matrix_sync(Cs[GATED ? 1 : 0] + rt * 16 * GGM_LDC + ct * 16, acc1, GGM_LDC, nvcuda::wmma::mem_row_major);
+    nvcuda::wmma::store_matrix_sync(Cs + rt * 16 * GGM_LDC + ct * 16, acc0, GGM_LDC, nvcuda::wmma::mem_row_major);
+    if (GATED) nvcuda::wmma::store_matrix_sync(Cs1 + rt * 16 * GGM_LDC + ct * 16, acc1, GGM_LDC, nvcuda::wmma::mem_row_major);
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      Cs[0][frow * GGM_LDC + fcg + 8 * j] = f0[j];
-      if (GATED) Cs[GATED ? 1 : 0][frow * GGM_LDC + fcg + 8 * j] = f1[j];
+      Cs[frow * GGM_LDC + fcg + 8 * j] = f0[j];
+      if (GATED) Cs1[frow * GGM_LDC + fcg + 8 * j] = f1[j];
     }
   }
   __syncthreads();
@@ -148,9 +199,9 @@ __global__ void __launch_bounds__(GGM_THREADS) grouped_gemm_kernel(GroupedArgs a
     if (r >= nrows || col >= a.Np) continue;
     float v = 0.f;
     if (col < N) {
-      v = Cs[0][r * GGM_LDC + c];
+      v = Cs[r * GGM_LDC + c];
       if (GATED) {
-        const float u = Cs[GATED ? 1 : 0][r * GGM_LDC + c];
+        const float u = Cs1[r * GGM_LDC + c];
         v = v / (1.f + expf(-v)) * u;
       }
       if (a.gate) {
@@ -179,12 +230,19 @@ extern "C" int gg_grouped_gemm(const void* A, long long lda, long long a_group_c
   const int row_tiles = offsets ? (M + GGM_BM - 1) / GGM_BM + G : (M + GGM_BM - 1) / GGM_BM;
   GG_REQUIRE(row_tiles <= 65535 && G <= 65535, "grouped_gemm: %d row tiles or %d groups are too many for one launch", row_tiles, G);
   dim3 grid((Np + GGM_BN - 1) / GGM_BN, row_tiles, offsets ? 1 : G);
+  const int esize = act_dtype == GG_F32 ? 4 : 2, vpt = 16 / esize;
+  const bool vec = K % vpt == 0 && lda % vpt == 0 && a_group_cols % vpt == 0 && ((size_t)A % 16) == 0 && ((size_t)W % 16) == 0;
+#define GGM_LAUNCH(T, BK)                                                                                      \
+  do {                                                                                                         \
+    if (gated && vec) gg_launch(grouped_gemm_kernel<T, true, BK, true>, grid, dim3(GGM_THREADS), 0, stream, a);        \
+    else if (gated) gg_launch(grouped_gemm_kernel<T, true, BK, false>, grid, dim3(GGM_THREADS), 0, stream, a);         \
+    else if (vec) gg_launch(grouped_gemm_kernel<T, false, BK, true>, grid, dim3(GGM_THREADS), 0, stream, a);           \
+    else gg_launch(grouped_gemm_kernel<T, false, BK, false>, grid, dim3(GGM_THREADS), 0, stream, a);                   \
+  } while (0)
   if (act_dtype == GG_F32) {
-    if (gated) gg_launch(grouped_gemm_kernel<float, true>, grid, dim3(GGM_THREADS), 0, stream, a);
-    else gg_launch(grouped_gemm_kernel<float, false>, grid, dim3(GGM_THREADS), 0, stream, a);
+    GGM_LAUNCH(float, 32);
   } else if (act_dtype == GG_BF16) {
-    if (gated) gg_launch(grouped_gemm_kernel<__nv_bfloat16, true>, grid, dim3(GGM_THREADS), 0, stream, a);
-    else gg_launch(grouped_gemm_kernel<__nv_bfloat16, false>, grid, dim3(GGM_THREADS), 0, stream, a);
+    GGM_LAUNCH(__nv_bfloat16, 128);
   } else {
     return gg_fail(GG_ERR_INVALID, "grouped_gemm: unknown dtype %d", act_dtype);
   }

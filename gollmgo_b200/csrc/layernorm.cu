@@ -14,6 +14,28 @@
 // taken about the mean in a second pass over the row held in shared memory.
 #include "common.cuh"
 
+// four values at a time (rows of a multiple of four values, 16-byte aligned in float32)
+template <typename TA> struct LnVec4;
+template <> struct LnVec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct LnVec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<unsigned*>(&a);
+    r.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
 template <typename TA>
 __global__ void add_norm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                                 const float* __restrict__ w, const float* __restrict__ b,
@@ -52,7 +74,7 @@ __global__ void add_norm_kernel(float* __restrict__ resid, const TA* __restrict_
   }
 }
 
-template <typename TA>
+template <typename TA, bool VEC>
 __global__ void norm_scale_add_kernel(float* __restrict__ resid, const TA* __restrict__ y,
                                       const float* __restrict__ w, const float* __restrict__ b,
                                       const float* __restrict__ scale, TA* __restrict__ copy, int H,
@@ -64,26 +86,48 @@ __global__ void norm_scale_add_kernel(float* __restrict__ resid, const TA* __res
   const size_t t = blockIdx.x;
   const TA* yr = y + t * H;
   float s = 0.f;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    const float x = to_f32(yr[c]);
-    xs[c] = x;
-    s += x;
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+      const float4 x = LnVec4<TA>::load(yr + c);
+      *reinterpret_cast<float4*>(xs + c) = x;
+      s += (x.x + x.y) + (x.z + x.w);
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const float x = to_f32(yr[c]);
+      xs[c] = x;
+      s += x;
+    }
   }
   const float mean = layer ? block_sum(s, red) / (float)H : 0.f;
   float ss = 0.f;
+  if (!layer) __syncthreads();                 // block_sum was the barrier between writing xs and reading it
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     const float dx = xs[c] - mean;
     ss += dx * dx;
   }
   const float rinv = rsqrtf(block_sum(ss, red) / (float)H + eps);
   float* xr = resid + t * H;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float n = (xs[c] - mean) * rinv * w[c];
-    if (b) n += b[c];
-    if (scale) n *= scale[c];
-    const float v = xr[c] + n;
-    xr[c] = v;
-    if (copy) copy[t * H + c] = from_f32<TA>(v);
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+      const float4 x = *reinterpret_cast<const float4*>(xs + c), g = *reinterpret_cast<const float4*>(w + c);
+      float4 n = make_float4((x.x - mean) * rinv * g.x, (x.y - mean) * rinv * g.y, (x.z - mean) * rinv * g.z, (x.w - mean) * rinv * g.w);
+      if (b) { const float4 q = *reinterpret_cast<const float4*>(b + c); n.x += q.x; n.y += q.y; n.z += q.z; n.w += q.w; }
+      if (scale) { const float4 q = *reinterpret_cast<const float4*>(scale + c); n.x *= q.x; n.y *= q.y; n.z *= q.z; n.w *= q.w; }
+      float4 v = *reinterpret_cast<const float4*>(xr + c);
+      v.x += n.x; v.y += n.y; v.z += n.z; v.w += n.w;
+      *reinterpret_cast<float4*>(xr + c) = v;
+      if (copy) LnVec4<TA>::store(copy + t * H + c, v);
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float n = (xs[c] - mean) * rinv * w[c];
+      if (b) n += b[c];
+      if (scale) n *= scale[c];
+      const float v = xr[c] + n;
+      xr[c] = v;
+      if (copy) copy[t * H + c] = from_f32<TA>(v);
+    }
   }
 }
 
@@ -138,14 +182,20 @@ extern "C" int gg_norm_scale_add(float* resid, const void* y, const float* w, co
   const size_t smem = (size_t)(H + 33) * sizeof(float);
   GG_REQUIRE(smem <= 227 * 1024, "norm_scale_add: width %d needs %zu B of shared memory", H, smem);
   int rc;
+  const size_t esz = act_dtype == GG_F32 ? 4 : 2;
+  const bool vec = H % 4 == 0 && ((size_t)resid % 16) == 0 && ((size_t)w % 16) == 0 && ((size_t)b % 16) == 0 &&
+                   ((size_t)scale % 16) == 0 && ((size_t)y % (4 * esz)) == 0 && ((size_t)copy % (4 * esz)) == 0;
+  const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : norm_threads(H);
+#define NSA_LAUNCH(T_, V_)                                                                                    \
+  do {                                                                                                        \
+    if ((rc = norm_smem(norm_scale_add_kernel<T_, V_>, smem, "norm_scale_add"))) return rc;                   \
+    gg_launch(norm_scale_add_kernel<T_, V_>, dim3(T), dim3(threads), smem, stream, resid, (const T_*)y, w, b, \
+              scale, (T_*)copy, H, eps, layer);                                                               \
+  } while (0)
   if (act_dtype == GG_F32) {
-    if ((rc = norm_smem(norm_scale_add_kernel<float>, smem, "norm_scale_add"))) return rc;
-    gg_launch(norm_scale_add_kernel<float>, dim3(T), dim3(norm_threads(H)), smem, stream, resid, (const float*)y, w, b,
-              scale, (float*)copy, H, eps, layer);
+    if (vec) NSA_LAUNCH(float, true); else NSA_LAUNCH(float, false);
   } else if (act_dtype == GG_BF16) {
-    if ((rc = norm_smem(norm_scale_add_kernel<__nv_bfloat16>, smem, "norm_scale_add"))) return rc;
-    gg_launch(norm_scale_add_kernel<__nv_bfloat16>, dim3(T), dim3(norm_threads(H)), smem, stream, resid,
-              (const __nv_bfloat16*)y, w, b, scale, (__nv_bfloat16*)copy, H, eps, layer);
+    if (vec) NSA_LAUNCH(__nv_bfloat16, true); else NSA_LAUNCH(__nv_bfloat16, false);
   } else {
     return gg_fail(GG_ERR_INVALID, "norm_scale_add: unknown dtype %d", act_dtype);
   }

@@ -601,11 +601,39 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
 
 
 def moe_align(idx: torch.Tensor, n: int, experts: int, offsets: torch.Tensor, order: torch.Tensor,
-              place: torch.Tensor) -> None:
-    """The n (token, choice) pairs of idx sorted by expert: offsets [experts + 1], order [n] (pair
-    index at each place), place [n] (place of each pair)."""
-    _cuda(idx, offsets, order, place)
-    _check(lib().gg_moe_align(_p(idx), n, experts, _p(offsets), _p(order), _p(place), _stream()))
+              place: torch.Tensor, pad: int = 1, tile_group: Optional[torch.Tensor] = None) -> None:
+    """The n (token, choice) pairs of idx sorted by expert: offsets [experts + 1], order (pair
+    index at each place), place [n] (place of each pair).  ``pad`` > 1: every expert's places start
+    at a multiple of pad; order then has n + experts * (pad - 1) entries or more, -1 at places
+    that hold no pair, and tile_group[i] is the expert of places pad * i .. (or -1)."""
+    _cuda(idx, offsets, order, place, tile_group)
+    _check(lib().gg_moe_align(_p(idx), n, experts, int(pad), order.numel(), _p(offsets), _p(order), _p(place),
+                              _p(tile_group), tile_group.numel() if tile_group is not None else 0, _stream()))
+
+
+def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[p] = x[order[p] // top] where order[p] >= 0, zeros elsewhere."""
+    _cuda(x, order, out)
+    if out.dtype != x.dtype or out.shape[1] != x.shape[1] or out.shape[0] != order.numel():
+        raise KernelError("moe_gather: one row of x's width and dtype per place")
+    _check(lib().gg_moe_gather(_p(x), _p(order), order.numel(), int(top), x.shape[1], _p(out), dtype_code(x.dtype), _stream()))
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, groups: int,
+                    gated: bool = False) -> None:
+    """The tcgen05 product (gemm_tc) over groups: rows 128 i .. of x belong to group tile_group[i]
+    (< 0: to none, skipped) and are multiplied with that group's matrix w[g] ([groups, N, K]; gated:
+    [groups, 2N, K], out = silu(x Wg^T) * (x Wu^T)).  bfloat16; rows of x a multiple of 128."""
+    global tc_launched
+    M, K = x.shape
+    N = out.shape[1]
+    if w.numel() != groups * (2 if gated else 1) * N * K or out.shape[0] != M or not out.is_contiguous() \
+            or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_grouped: shapes or dtypes do not fit")
+    _cuda(w, out, tile_group)
+    tc_launched = True
+    _check(lib().gg_gemm_tc_grouped(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K, 2 if gated else 0,
+                                    _p(tile_group), groups, _p(tc_status(x.device)), _stream()))
 
 
 def moe_combine(y: torch.Tensor, place: torch.Tensor, wgt: torch.Tensor, shared: Optional[torch.Tensor],

@@ -200,7 +200,7 @@ def step_timeline(args) -> None:
     eng = Engine(config=cfg, weights_seed=0, engine_config=ecfg)
     runner = eng.runner
     gen = torch.Generator().manual_seed(1)
-    V = cfg["vocab_size"]
+    V = runner.spec.vocab_size
     rp = lambda k: torch.randint(0, V, (k,), generator=gen).tolist()
     if T:
         def one(i=[0]):

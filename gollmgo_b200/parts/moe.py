@@ -5,8 +5,9 @@ shared expert (any registered feed-forward) runs for every token and is added.
 Router: logits = x Wr^T + b in float32; the ``top`` largest are chosen and weighted by the
 softmax over the chosen logits alone.  Everything happens on the device (csrc/moe.cu): the
 (token, choice) pairs are sorted by expert there, two grouped products (csrc/grouped_gemm.cu) run
-every expert over its own rows (first product with the gate's activation in its epilogue), and a
-last kernel sums each token's results in float32.  No count ever reaches the host, so a step of
+every expert over its own rows (first product with the gate's activation in its epilogue; long
+steps in bfloat16 take the tcgen05 product of csrc/gemm_tc.cu over rows gathered into whole tiles
+per expert), and a last kernel sums each token's results in float32.  No count ever reaches the host, so a step of
 decoded tokens is captured like any other.
 
 params: hidden_size, intermediate_size, experts, top, router_bias (bool), shared (a feed-forward
@@ -17,9 +18,18 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from ..csrc import ops
 from ..weights import WeightSpec
+from .linear import GEMM_POLICY
 from .registry import build_feed_forward, register_feed_forward
+
+# Steps with at least this many (token, choice) pairs run the experts' products on tcgen05
+# (csrc/gemm_tc.cu, grouped): every expert's rows gathered into a block that starts at a multiple
+# of the product's tile height.  Below, a tile of 128 rows would be mostly padding.
+TC_MIN_PAIRS = int(os.environ.get("GOLLMGO_B200_MOE_TC_PAIRS", "1024"))
+TC_TILE = 128
 
 DEFAULT_NAMES = {"router": "router", "router_bias": "router.b", "expert": "e{e}.", "gate": "gate",
                  "up": "up", "down": "down", "shared": "shared."}
@@ -43,15 +53,24 @@ class MixtureOfExperts:
         self.shared = build_feed_forward(shared, ctx) if shared is not None else None
         ws, T = ctx.workspace, ctx.max_tokens
         n = T * self.top
+        self.tc_ok = (ctx.act_dtype == torch.bfloat16 and GEMM_POLICY != "lib" and self.hidden % 8 == 0
+                      and self.inter % 8 == 0 and ctx.device.type == "cuda")
+        slots = self._slots(n) if self.tc_ok and n >= TC_MIN_PAIRS else n
         ws.reserve("moe_idx", n, torch.int32)
         ws.reserve("moe_wgt", n, torch.float32)
-        ws.reserve("moe_order", n, torch.int32)
+        ws.reserve("moe_order", slots, torch.int32)
         ws.reserve("moe_place", n, torch.int32)
         ws.reserve("moe_offsets", self.experts + 1, torch.int32)
-        ws.reserve("moe_act", n * self.inter, ctx.act_dtype)
-        ws.reserve("moe_rows", n * self.hidden, ctx.act_dtype)
+        ws.reserve("moe_tiles", slots // TC_TILE + 1, torch.int32)
+        ws.reserve("moe_in", slots * self.hidden, ctx.act_dtype)
+        ws.reserve("moe_act", slots * self.inter, ctx.act_dtype)
+        ws.reserve("moe_rows", slots * self.hidden, ctx.act_dtype)
         ws.reserve("moe_out", T * self.hidden, ctx.act_dtype)
         self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def _slots(self, n):
+        """Places of the padded row block: every expert's rows rounded up to whole tiles."""
+        return (-(-n // TC_TILE) + self.experts) * TC_TILE
 
     def _expert(self, e, which):
         return self.names["expert"].format(e=e) + self.names[which]
@@ -89,14 +108,27 @@ class MixtureOfExperts:
         T, ws = x.shape[0], self.ctx.workspace
         n, E = T * self.top, self.experts
         idx, wgt = self.route(x)
-        order, place = ws.get("moe_order", 1, n), ws.get("moe_place", 1, n)
+        place = ws.get("moe_place", 1, n)
         offsets = ws.get("moe_offsets", 1, E + 1)
-        ops.moe_align(idx, n, E, offsets, order, place)
-        a = ws.get("moe_act", n, self.inter)
-        ops.grouped_gemm(x, self.w_gate_up, a, self.inter, self.hidden, E, offsets=offsets, row_index=order,
-                         row_div=self.top, rows=n, gated=True)
-        y = ws.get("moe_rows", n, self.hidden)
-        ops.grouped_gemm(a, self.w_down, y, self.hidden, self.inter, E, offsets=offsets, rows=n)
+        if self.tc_ok and n >= TC_MIN_PAIRS and x.is_contiguous():
+            # a long step: rows gathered by expert into whole tiles, both products on tcgen05
+            slots = self._slots(n)
+            order, tiles = ws.get("moe_order", 1, slots), ws.get("moe_tiles", 1, slots // TC_TILE)
+            ops.moe_align(idx, n, E, offsets, order, place, pad=TC_TILE, tile_group=tiles)
+            xin = ws.get("moe_in", slots, self.hidden)
+            ops.moe_gather(x, order, self.top, xin)
+            a = ws.get("moe_act", slots, self.inter)
+            ops.gemm_tc_grouped(xin, self.w_gate_up, a, tiles, E, gated=True)
+            y = ws.get("moe_rows", slots, self.hidden)
+            ops.gemm_tc_grouped(a, self.w_down, y, tiles, E)
+        else:
+            order = ws.get("moe_order", 1, n)
+            ops.moe_align(idx, n, E, offsets, order, place)
+            a = ws.get("moe_act", n, self.inter)
+            ops.grouped_gemm(x, self.w_gate_up, a, self.inter, self.hidden, E, offsets=offsets, row_index=order,
+                             row_div=self.top, rows=n, gated=True)
+            y = ws.get("moe_rows", n, self.hidden)
+            ops.grouped_gemm(a, self.w_down, y, self.hidden, self.inter, E, offsets=offsets, rows=n)
         shared = self.shared.forward(x, batch) if self.shared is not None else None
         out = ws.get("moe_out", T, self.hidden)
         ops.moe_combine(y, place, wgt, shared, out, self.top)

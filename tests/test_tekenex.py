@@ -124,15 +124,20 @@ def test_router(kit, dtype, experts, top):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("experts,top,shared,T", [(6, 2, 24, 37), (4, 1, 0, 5), (3, 3, 40, 1), (12, 2, 16, 150)])
+@pytest.mark.parametrize("experts,top,shared,T", [(6, 2, 24, 37), (4, 1, 0, 5), (3, 3, 40, 1), (12, 2, 16, 150),
+                                                  (6, 2, 24, 700), (20, 3, 0, 400)])
 def test_mixture_of_experts(kit, dtype, experts, top, shared, T):
+    """Few rows (the kernel that streams the chosen experts' weights) and many rows (in bfloat16 the
+    tcgen05 product over rows gathered into whole tiles per expert, some experts with no row at all)."""
     torch.manual_seed(4)
     D, F = 40, 24
     sh = kit.parts.PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": shared, "names": ("gate", "up", "down")}) \
         if shared else None
     moe = kit.parts.build_feed_forward(kit.parts.PartSpec("moe", {"hidden_size": D, "intermediate_size": F, "experts": experts,
-                                                                   "top": top, "shared": sh}), ctx_for(kit, dtype))
+                                                                   "top": top, "shared": sh}), ctx_for(kit, dtype, max_tokens=1024))
     p = {"router": bf(torch.randn(experts, D) / 3), "router.b": bf(torch.randn(experts) / 2)}
+    if experts == 20:
+        p["router.b"][15:] = -100.0                  # experts that no token ever picks
     for e in [f"e{i}." for i in range(experts)] + (["shared."] if shared else []):
         f = shared if e == "shared." else F
         p.update({e + "gate": bf(torch.randn(f, D) / 6), e + "up": bf(torch.randn(f, D) / 6), e + "down": bf(torch.randn(D, f) / 5)})
