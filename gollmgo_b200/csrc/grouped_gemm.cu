@@ -50,7 +50,7 @@ template <> struct GgmZero<__nv_bfloat16> { static __device__ __forceinline__ __
 // the products of this one, which hides most of a trip to memory when a group has only a few
 // rows and the kernel streams its weights (decoded tokens).
 template <typename TA, bool GATED, int BK, bool VEC>
-__global__ void __launch_bounds__(GGM_THREADS) grouped_gemm_kernel(GroupedArgs a) {
+__global__ void __launch_bounds__(GGM_THREADS, (sizeof(TA) == 2 ? (GATED ? 2 : 4) : 1)) grouped_gemm_kernel(GroupedArgs a) {
   constexpr int LD = BK + 8;
   constexpr int NB = GATED ? 2 : 1;
   constexpr int VPT = 16 / (int)sizeof(TA);                     // values in a 16-byte chunk

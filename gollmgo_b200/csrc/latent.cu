@@ -51,6 +51,42 @@ extern "C" int gg_latent_norm_write(const void* src, long long src_stride, int c
   return gg_check_launch("latent_norm_write");
 }
 
+// a[t, h * n .. h * n + n) *= sigmoid(gates[t, col0 + h]): the output gate of an attention head, for
+// steps whose per-head products ran in the vendor library.
+template <typename TA>
+__global__ void head_gate_kernel(TA* __restrict__ a, const TA* __restrict__ gates, long long ldg, int col0, int H, int n) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float gs[1024];                     // the token's gates, sigmoid applied (launcher: H <= 1024)
+  const size_t t = blockIdx.x;
+  const int w = H * n;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) gs[h] = 1.f / (1.f + expf(-to_f32(gates[t * ldg + col0 + h])));
+  __syncthreads();
+  if (n % 2 == 0 && sizeof(TA) == 2) {           // bfloat16 pairs: both values of a pair belong to one head
+    __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(a + t * w);
+    for (int c = threadIdx.x; c < w / 2; c += blockDim.x) {
+      const float g = gs[(2 * c) / n];
+      const float2 v = __bfloat1622float2(row[c]);
+      row[c] = __floats2bfloat162_rn(v.x * g, v.y * g);
+    }
+    return;
+  }
+  for (int c = threadIdx.x; c < w; c += blockDim.x) a[t * w + c] = from_f32<TA>(to_f32(a[t * w + c]) * gs[c / n]);
+}
+
+extern "C" int gg_head_gate(void* a, const void* gates, long long ldg, int col0, int T, int H, int n, int act_dtype,
+                            cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && H <= 1024 && n > 0 && a && gates, "head_gate: bad arguments (at most 1024 heads)");
+  if (T == 0) return GG_OK;
+  if (act_dtype == GG_F32)
+    gg_launch(head_gate_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)a, (const float*)gates, ldg, col0, H, n);
+  else if (act_dtype == GG_BF16)
+    gg_launch(head_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)a, (const __nv_bfloat16*)gates, ldg, col0, H, n);
+  else
+    return gg_fail(GG_ERR_INVALID, "head_gate: unknown dtype %d", act_dtype);
+  return gg_check_launch("head_gate");
+}
+
 // kind 0: relu(z)^2;  1: gelu, tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));  2: silu
 enum { GG_ACT_RELU2 = 0, GG_ACT_GELU_TANH = 1, GG_ACT_SILU = 2 };
 
@@ -68,10 +104,36 @@ __global__ void act_kernel(const TA* __restrict__ in, TA* __restrict__ out, size
     out[e] = from_f32<TA>(act_apply(to_f32(in[e]), kind));
 }
 
+// 16 bytes a thread (n a multiple of the chunk, both pointers 16-byte aligned)
+template <typename TA>
+__global__ void act_vec_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, size_t chunks, int kind) {
+  constexpr int VPT = 16 / (int)sizeof(TA);
+  pdl_trigger();
+  pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < chunks; e += (size_t)gridDim.x * blockDim.x) {
+    uint4 r = in[e];
+    TA* v = reinterpret_cast<TA*>(&r);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) v[j] = from_f32<TA>(act_apply(to_f32(v[j]), kind));
+    out[e] = r;
+  }
+}
+
 extern "C" int gg_act(const void* in, void* out, int act_dtype, long long n, int kind, cudaStream_t stream) {
   GG_REQUIRE(n >= 0 && in && out, "act: bad arguments");
   GG_REQUIRE(kind >= 0 && kind <= 2, "act: unknown activation %d", kind);
   if (n == 0) return GG_OK;
+  const int vpt = act_dtype == GG_F32 ? 4 : 8;
+  if ((act_dtype == GG_F32 || act_dtype == GG_BF16) && n % vpt == 0 && ((size_t)in % 16) == 0 && ((size_t)out % 16) == 0) {
+    const long long chunks = n / vpt;
+    long long vb = (chunks + 255) / 256;
+    if (vb > 148 * 32) vb = 148 * 32;
+    if (act_dtype == GG_F32)
+      gg_launch(act_vec_kernel<float>, dim3((int)vb), dim3(256), 0, stream, (const uint4*)in, (uint4*)out, (size_t)chunks, kind);
+    else
+      gg_launch(act_vec_kernel<__nv_bfloat16>, dim3((int)vb), dim3(256), 0, stream, (const uint4*)in, (uint4*)out, (size_t)chunks, kind);
+    return gg_check_launch("act");
+  }
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (act_dtype == GG_F32)

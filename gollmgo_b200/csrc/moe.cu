@@ -13,60 +13,81 @@
 #define MOE_MAX_EXPERTS 1024
 #define MOE_MAX_TOP 32
 
-// dot of the staged row xs[0..D) with one router row, over the lanes of a warp
-__device__ __forceinline__ float route_dot(const float* xs, const float* w, int D, int lane, bool vec) {
-  float s = 0.f;
-  if (vec) {
-    for (int c = lane * 4; c < D; c += 128) {
-      const float4 a = *reinterpret_cast<const float4*>(xs + c), b = *reinterpret_cast<const float4*>(w + c);
-      s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
-    }
-  } else {
-    for (int c = lane; c < D; c += 32) s = fmaf(xs[c], w[c], s);
-  }
-  return s;
+// A block routes ROUTE_TOK tokens: their rows are staged in shared memory as float32, and a warp
+// that takes an expert reads that expert's router row once (16 bytes a lane at a time) for all of
+// them, so the router's weights cross from L2 once per ROUTE_TOK tokens and not once per token.
+#define ROUTE_TOK 4      // for steps of many tokens; steps of a few tokens take one token a block, for more blocks
+
+__device__ __forceinline__ void route_load(const float* w, float (&v)[8], int n) {
+  const float4 a = *reinterpret_cast<const float4*>(w);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  (void)n;
 }
-__device__ __forceinline__ float route_dot(const float* xs, const __nv_bfloat16* w, int D, int lane, bool vec) {
-  float s = 0.f;
-  if (vec) {
-    for (int c = lane * 8; c < D; c += 256) {
-      const uint4 r = *reinterpret_cast<const uint4*>(w + c);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
-      const float4 x0 = *reinterpret_cast<const float4*>(xs + c), x1 = *reinterpret_cast<const float4*>(xs + c + 4);
-      const float2 b0 = __bfloat1622float2(p[0]), b1 = __bfloat1622float2(p[1]);
-      const float2 b2 = __bfloat1622float2(p[2]), b3 = __bfloat1622float2(p[3]);
-      s = fmaf(x0.x, b0.x, s); s = fmaf(x0.y, b0.y, s); s = fmaf(x0.z, b1.x, s); s = fmaf(x0.w, b1.y, s);
-      s = fmaf(x1.x, b2.x, s); s = fmaf(x1.y, b2.y, s); s = fmaf(x1.z, b3.x, s); s = fmaf(x1.w, b3.y, s);
-    }
-  } else {
-    for (int c = lane; c < D; c += 32) s = fmaf(xs[c], __bfloat162float(w[c]), s);
-  }
-  return s;
+__device__ __forceinline__ void route_load(const __nv_bfloat16* w, float (&v)[8], int n) {
+  const uint4 r = *reinterpret_cast<const uint4*>(w);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 b = __bfloat1622float2(p[j]); v[2 * j] = b.x; v[2 * j + 1] = b.y; }
+  (void)n;
 }
 
-template <typename TA>
+template <typename TA, int TOK>
 __global__ void moe_route_kernel(const TA* __restrict__ h, const TA* __restrict__ wr, const float* __restrict__ bias,
-                                 int D, int E, int top, int* __restrict__ idx, float* __restrict__ wgt, int vec) {
-  __shared__ float z[MOE_MAX_EXPERTS];
-  extern __shared__ __align__(16) float xs[];              // the token's row, D floats
+                                 int T, int D, int E, int top, int* __restrict__ idx, float* __restrict__ wgt, int vec) {
+  __shared__ float z[TOK][MOE_MAX_EXPERTS];
+  extern __shared__ __align__(16) float xs[];              // TOK rows of D floats
+  constexpr int VPT = 16 / (int)sizeof(TA);
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const TA* x = h + (size_t)t * D;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) xs[c] = to_f32(x[c]);
-  __syncthreads();
-  for (int e = warp; e < E; e += nw) {
-    const float s = warp_sum(route_dot(xs, wr + (size_t)e * D, D, lane, vec != 0));
-    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int nt = min(TOK, T - t0);
+  for (int e = threadIdx.x; e < TOK * D; e += blockDim.x) {
+    const int r = e / D;
+    xs[e] = r < nt ? to_f32(h[(size_t)(t0 + r) * D + (e - r * D)]) : 0.f;
   }
   __syncthreads();
-  if (warp == 0) {
+  for (int e = warp; e < E; e += nw) {
+    const TA* w = wr + (size_t)e * D;
+    float s[TOK];
+#pragma unroll
+    for (int r = 0; r < TOK; ++r) s[r] = 0.f;
+    if (vec) {
+      for (int c = lane * VPT; c < D; c += 32 * VPT) {
+        float v[8];
+        route_load(w + c, v, VPT);
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) {
+#pragma unroll
+          for (int j = 0; j < VPT; j += 4) {                // the staged rows four values at a time
+            const float4 x = *reinterpret_cast<const float4*>(xs + r * D + c + j);
+            s[r] = fmaf(x.x, v[j], s[r]); s[r] = fmaf(x.y, v[j + 1], s[r]);
+            s[r] = fmaf(x.z, v[j + 2], s[r]); s[r] = fmaf(x.w, v[j + 3], s[r]);
+          }
+        }
+      }
+    } else {
+      for (int c = lane; c < D; c += 32) {
+        const float v = to_f32(w[c]);
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) s[r] = fmaf(xs[r * D + c], v, s[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < TOK; ++r) {
+      const float tot = warp_sum(s[r]);
+      if (lane == 0) z[r][e] = tot + (bias ? bias[e] : 0.f);
+    }
+  }
+  __syncthreads();
+  if (warp < nt) {                                         // warp r picks for token t0 + r (the block has TOK warps or more)
+    const int t = t0 + warp;
+    float* zr = z[warp];
     float val[MOE_MAX_TOP];
     for (int j = 0; j < top; ++j) {
       float best = -INFINITY;
       int bi = 0x7fffffff;
       for (int e = lane; e < E; e += 32) {
-        const float v = z[e];
+        const float v = zr[e];
         if (v > best || (v == best && e < bi)) { best = v; bi = e; }
       }
 #pragma unroll
@@ -77,7 +98,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ h, const TA* __restrict_
       }
       if (bi == 0x7fffffff) bi = 0;                  // every logit left is -inf or NaN
       val[j] = best;
-      if (lane == 0) { idx[(size_t)t * top + j] = bi; z[bi] = -INFINITY; }
+      if (lane == 0) { idx[(size_t)t * top + j] = bi; zr[bi] = -INFINITY; }
       __syncwarp();
     }
     if (lane == 0) {
@@ -86,6 +107,46 @@ __global__ void moe_route_kernel(const TA* __restrict__ h, const TA* __restrict_
       for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - m); sum += val[j]; }
       for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] = val[j] / sum;
     }
+  }
+}
+
+// The choice alone, from logits a product has already made (long steps: z = h Wr^T in float32 by the
+// vendor library from the bfloat16 rows): one warp a token adds the bias, picks and weighs.
+__global__ void moe_topk_kernel(const float* __restrict__ z, const float* __restrict__ bias, int T, int E, int top,
+                                int* __restrict__ idx, float* __restrict__ wgt) {
+  extern __shared__ float zs[];                            // warps x E
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* zr = zs + warp * E;
+  for (int e = lane; e < E; e += 32) zr[e] = z[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  float val[MOE_MAX_TOP];
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = zr[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) bi = 0;
+    val[j] = best;
+    if (lane == 0) { idx[(size_t)t * top + j] = bi; zr[bi] = -INFINITY; }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float m = val[0];
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) { val[j] = expf(val[j] - m); sum += val[j]; }
+    for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] = val[j] / sum;
   }
 }
 
@@ -196,20 +257,36 @@ extern "C" int gg_moe_route(const void* h, const void* wr, const float* bias, in
              MOE_MAX_EXPERTS, MOE_MAX_TOP, E, top);
   GG_REQUIRE(h && wr && idx && wgt, "moe_route: a pointer is null");
   if (T == 0) return GG_OK;
-  const size_t smem = (size_t)D * sizeof(float);
-  GG_REQUIRE(smem <= 160 * 1024, "moe_route: rows of %d values do not fit in shared memory", D);
+  const int tok = T > 256 ? ROUTE_TOK : 1;
+  const size_t smem = (size_t)tok * D * sizeof(float);
+  GG_REQUIRE(smem <= 200 * 1024, "moe_route: rows of %d values do not fit in shared memory", D);
   const int vec = (act_dtype == GG_F32 ? D % 4 == 0 : D % 8 == 0) && ((size_t)wr % 16) == 0;
-  const int threads = E >= 8 ? 256 : 128;
+  const int threads = E >= 8 ? 256 : 128;                  // at least ROUTE_TOK warps
+  const int blocks = (T + tok - 1) / tok;
+#define ROUTE_LAUNCH(T_, N_)                                                                                     \
+  do {                                                                                                           \
+    if (smem > 28 * 1024) cudaFuncSetAttribute(moe_route_kernel<T_, N_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    gg_launch(moe_route_kernel<T_, N_>, dim3(blocks), dim3(threads), smem, stream, (const T_*)h, (const T_*)wr, bias, T, D, E, top, idx, wgt, vec); \
+  } while (0)
   if (act_dtype == GG_F32) {
-    if (smem > 44 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gg_launch(moe_route_kernel<float>, dim3(T), dim3(threads), smem, stream, (const float*)h, (const float*)wr, bias, D, E, top, idx, wgt, vec);
+    if (tok == 1) ROUTE_LAUNCH(float, 1); else ROUTE_LAUNCH(float, ROUTE_TOK);
   } else if (act_dtype == GG_BF16) {
-    if (smem > 44 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gg_launch(moe_route_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)wr,
-              bias, D, E, top, idx, wgt, vec);
+    if (tok == 1) ROUTE_LAUNCH(__nv_bfloat16, 1); else ROUTE_LAUNCH(__nv_bfloat16, ROUTE_TOK);
   } else
     return gg_fail(GG_ERR_INVALID, "moe_route: unknown dtype %d", act_dtype);
   return gg_check_launch("moe_route");
+}
+
+extern "C" int gg_moe_topk(const float* z, const float* bias, int T, int E, int top, int* idx, float* wgt,
+                           cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && E > 0 && top > 0 && top <= E && E <= MOE_MAX_EXPERTS && top <= MOE_MAX_TOP,
+             "moe_topk: bad sizes T=%d E=%d top=%d", T, E, top);
+  GG_REQUIRE(z && idx && wgt, "moe_topk: a pointer is null");
+  if (T == 0) return GG_OK;
+  const int warps = 4;
+  gg_launch(moe_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), (size_t)warps * E * sizeof(float), stream,
+            z, bias, T, E, top, idx, wgt);
+  return gg_check_launch("moe_topk");
 }
 
 extern "C" int gg_moe_align(const int* idx, int n, int E, int pad, int slots, int* offsets, int* sorted, int* place,

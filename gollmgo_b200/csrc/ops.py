@@ -583,6 +583,16 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, k:
                                  dtype_code(a.dtype), _stream()))
 
 
+def head_gate(a: torch.Tensor, gates: torch.Tensor, col0: int, heads: int) -> None:
+    """a[t, h * n : h * n + n] *= sigmoid(gates[t, col0 + h]) in place (a [T, heads * n] contiguous)."""
+    _cuda(a)
+    T, w = a.shape
+    if w % heads or gates.dtype != a.dtype or gates.stride(-1) != 1:
+        raise KernelError("head_gate: a is [T, heads * n], the gates of its dtype")
+    _check(lib().gg_head_gate(_p(a), _p(gates), ctypes.c_longlong(gates.stride(0)), int(col0), T, heads, w // heads,
+                              dtype_code(a.dtype), _stream()))
+
+
 # ---------------------------------------------------------------- mixture of experts
 MOE_MAX_EXPERTS, MOE_MAX_TOP = 1024, 32
 
@@ -598,6 +608,14 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
             or (bias is not None and bias.dtype != torch.float32):
         raise KernelError("moe_route: router of the rows' dtype, bias and weights float32, choices int32")
     _check(lib().gg_moe_route(_p(h), _p(w_router), _p(bias), T, D, E, top, _p(idx), _p(wgt), dtype_code(h.dtype), _stream()))
+
+
+def moe_topk(z: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, wgt: torch.Tensor) -> None:
+    """moe_route's choice from logits z [T, E] (float32) that a product has already made."""
+    _cuda(z, bias, idx, wgt)
+    if z.dtype != torch.float32 or idx.dtype != torch.int32 or wgt.dtype != torch.float32:
+        raise KernelError("moe_topk: logits and weights float32, choices int32")
+    _check(lib().gg_moe_topk(_p(z), _p(bias), z.shape[0], z.shape[1], top, _p(idx), _p(wgt), _stream()))
 
 
 def moe_align(idx: torch.Tensor, n: int, experts: int, offsets: torch.Tensor, order: torch.Tensor,

@@ -5,6 +5,7 @@ on inputs larger than L2 (a ring of weight copies, or a cache of many sequences)
     python -m gollmgo_b200.microbench gemm_tc      [--tokens 2048]
     python -m gollmgo_b200.microbench attn_decode  [--batch 64] [--context 2048]
     python -m gollmgo_b200.microbench attn_prefill [--tokens 2048]
+    python -m gollmgo_b200.microbench grouped_gemm  [--tokens 8 --experts 16 --top 2 --hidden 2048 --intermediate 1024]
     python -m gollmgo_b200.microbench step_timeline [--batch 8] [--context 2048] [--prompt-tokens 0]
 
 Sizes default to the Llama-3.1-8B shape.  With ``--reps 2`` a run is short enough to
@@ -175,6 +176,33 @@ def sample(args) -> None:
         print(f"sample ({name}) rows={B} vocab={V}: {t:7.1f} us", flush=True)
 
 
+def grouped_gemm(args) -> None:
+    """The products of a mixture of experts at decode size: --tokens tokens, each with --top of
+    --experts experts (choices spread evenly), width --hidden, experts' width --intermediate.  The
+    bytes are the weights of the experts that got a row, read once; several copies of the weights
+    are walked so that no launch finds them in L2."""
+    T, E, top, D, F = args.tokens, args.experts, args.top, args.hidden, args.intermediate
+    n = T * top
+    idx = (torch.arange(n, device="cuda", dtype=torch.int32) * 7 % E).contiguous()
+    used = len(set(idx.tolist()))
+    offsets = torch.empty(E + 1, device="cuda", dtype=torch.int32)
+    order, place = torch.empty(n, device="cuda", dtype=torch.int32), torch.empty(n, device="cuda", dtype=torch.int32)
+    ops.moe_align(idx, n, E, offsets, order, place)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    a = torch.empty(n, F, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(n, D, device="cuda", dtype=torch.bfloat16)
+    wbytes = E * 3 * F * D * 2
+    copies = max(2, int(3 * L2_BYTES // wbytes) + 1)
+    gu = [torch.randn(E, 2 * F, D, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    dn = [torch.randn(E, D, F, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    t1 = _time(lambda i: ops.grouped_gemm(x, gu[i % copies], a, F, D, E, offsets=offsets, row_index=order, row_div=top,
+                                          rows=n, gated=True), args.reps)
+    t2 = _time(lambda i: ops.grouped_gemm(a, dn[i % copies], y, D, F, E, offsets=offsets, rows=n), args.reps)
+    b1, b2 = used * 2 * F * D * 2, used * D * F * 2
+    print(f"grouped_gemm gate_up+silu  {n} pairs on {used} of {E} experts, {F}x{D}: {t1:7.1f} us  {b1 / t1 / 1e3:7.1f} GB/s")
+    print(f"grouped_gemm down          {n} pairs on {used} of {E} experts, {D}x{F}: {t2:7.1f} us  {b2 / t2 / 1e3:7.1f} GB/s")
+
+
 def step_timeline(args) -> None:
     """Kernel timeline of one step of the whole model through CUPTI (torch.profiler): per kernel
     name the launches of the step, their summed durations and the idle time before them.  A
@@ -244,7 +272,7 @@ def step_timeline(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m gollmgo_b200.microbench")
-    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill", "sample", "step_timeline"])
+    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attn_decode", "attn_prefill", "sample", "step_timeline", "grouped_gemm"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=2048)
@@ -257,13 +285,15 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--experts", type=int, default=16, help="grouped_gemm: experts of the mixture")
+    ap.add_argument("--top", type=int, default=2, help="grouped_gemm: experts a token")
     ap.add_argument("--shape", default="llama_3_1_8b", help="step_timeline: a file of bench_shapes/")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="step_timeline: a prompt step of so many tokens instead of a decode step")
     args = ap.parse_args(argv)
     if args.tokens is None:
         args.tokens = 8 if args.kernel == "gemm_small_m" else 2048
     {"gemm_small_m": gemm_small_m, "gemm_tc": gemm_tc, "attn_decode": attn_decode, "attn_prefill": attn_prefill,
-     "sample": sample, "step_timeline": step_timeline}[args.kernel](args)
+     "sample": sample, "step_timeline": step_timeline, "grouped_gemm": grouped_gemm}[args.kernel](args)
     return 0
 
 

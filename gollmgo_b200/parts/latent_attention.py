@@ -17,17 +17,25 @@ latent's norm), gate (bool), names: dict of the tensors' local names.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..cache import PagedKVNeed
 from ..csrc import ops
 from ..weights import WeightSpec
 from .attention import ATTN_POLICY, TILES_GENERAL, TILES_MMA, TILES_TC, context_tiles, decode_splits, TILE_KEYS, MAX_TILES
-from .linear import linear
+from .linear import GEMM_POLICY, linear
 from .registry import register_mixer
 
 DEFAULT_NAMES = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "gate": "g", "o": "o"}
 RANK_ALIGN = 16          # the latent's rows are padded to a multiple of this in the cache (zeros)
+# Steps of at least this many tokens (bfloat16, a latent that needs no padding) run the two per-head
+# products as batched products of the vendor library, as the other products of prompt steps are:
+# the grouped kernel's tiles of 32 rows are made for steps that stream the weights.  Measured on
+# a prompt step of 2048 tokens (16 heads, 64 -> 128 and 128 -> 128): 20 us a product with the
+# grouped kernel.
+BMM_MIN_TOKENS = int(os.environ.get("GOLLMGO_B200_LATENT_BMM_TOKENS", "256"))
 
 
 class LatentAttention:
@@ -130,8 +138,14 @@ class LatentAttention:
         if writes_cache:
             ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, batch.slot_mapping[group], kc)
         q = ws.get("lat_q", T, nh * Rp)
-        ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.dim, o_group_cols=Rp,
-                         n_padded=Rp, rows=T)
+        lib = (T >= BMM_MIN_TOKENS and Rp == R and self.ctx.act_dtype == torch.bfloat16 and GEMM_POLICY != "tc")
+        if lib:
+            # [heads, T, dim] @ [heads, dim, rank] -> [heads, T, rank], all three as views of the step's buffers
+            torch.bmm(proj[:, :nh * self.dim].view(T, nh, self.dim).transpose(0, 1), self.w_uk_t.transpose(1, 2),
+                      out=q.view(T, nh, Rp).transpose(0, 1))
+        else:
+            ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.dim, o_group_cols=Rp,
+                             n_padded=Rp, rows=T)
         o = ws.get("lat_o", T, nh * Rp)
         bt = batch.block_tables[group]
         ps = self.ctx.page_size
@@ -159,8 +173,13 @@ class LatentAttention:
                             ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, 1, Rp, ps, 0, self.scale,
                             allow_mma=self._fast())
         a = ws.get("attn_out", T, nh * self.vdim)
-        ops.grouped_gemm(o, self.w_uv, a, self.vdim, R, nh, a_group_cols=Rp, o_group_cols=self.vdim, rows=T,
-                         gate=proj if self.gated else None, gate_col0=self.col_g)
+        if lib:
+            torch.bmm(o.view(T, nh, Rp).transpose(0, 1), self.w_uv.transpose(1, 2), out=a.view(T, nh, self.vdim).transpose(0, 1))
+            if self.gated:
+                ops.head_gate(a, proj, self.col_g, nh)
+        else:
+            ops.grouped_gemm(o, self.w_uv, a, self.vdim, R, nh, a_group_cols=Rp, o_group_cols=self.vdim, rows=T,
+                             gate=proj if self.gated else None, gate_col0=self.col_g)
         return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
 
 

@@ -22,7 +22,7 @@ import os
 
 from ..csrc import ops
 from ..weights import WeightSpec
-from .linear import GEMM_POLICY
+from .linear import GEMM_POLICY, linear
 from .registry import build_feed_forward, register_feed_forward
 
 # Steps with at least this many (token, choice) pairs run the experts' products on tcgen05
@@ -30,6 +30,9 @@ from .registry import build_feed_forward, register_feed_forward
 # of the product's tile height.  Below, a tile of 128 rows would be mostly padding.
 TC_MIN_PAIRS = int(os.environ.get("GOLLMGO_B200_MOE_TC_PAIRS", "1024"))
 TC_TILE = 128
+# From this many tokens the router's logits are a product of the vendor library (bfloat16 rows, float32
+# accumulation and result) followed by the choice alone; below, one kernel does both from shared memory.
+ROUTE_LIB_TOKENS = int(os.environ.get("GOLLMGO_B200_MOE_ROUTE_LIB_TOKENS", "512"))
 
 DEFAULT_NAMES = {"router": "router", "router_bias": "router.b", "expert": "e{e}.", "gate": "gate",
                  "up": "up", "down": "down", "shared": "shared."}
@@ -56,6 +59,7 @@ class MixtureOfExperts:
         self.tc_ok = (ctx.act_dtype == torch.bfloat16 and GEMM_POLICY != "lib" and self.hidden % 8 == 0
                       and self.inter % 8 == 0 and ctx.device.type == "cuda")
         slots = self._slots(n) if self.tc_ok and n >= TC_MIN_PAIRS else n
+        ws.reserve("moe_logits", T * self.experts, torch.float32)
         ws.reserve("moe_idx", n, torch.int32)
         ws.reserve("moe_wgt", n, torch.float32)
         ws.reserve("moe_order", slots, torch.int32)
@@ -101,7 +105,13 @@ class MixtureOfExperts:
         """(choices [T, top] int32, weights [T, top] float32) of the rows x."""
         T, ws = x.shape[0], self.ctx.workspace
         idx, wgt = ws.get("moe_idx", T, self.top), ws.get("moe_wgt", T, self.top)
-        ops.moe_route(x, self.w_router, self.b_router, self.top, idx, wgt)
+        if T >= ROUTE_LIB_TOKENS and x.dtype == torch.bfloat16:
+            # a long step: the logits are a product like any other (bfloat16 rows, float32 sums and result)
+            z = ws.get("moe_logits", T, self.experts)
+            linear(x, self.w_router, z)
+            ops.moe_topk(z, self.b_router, self.top, idx, wgt)
+        else:
+            ops.moe_route(x, self.w_router, self.b_router, self.top, idx, wgt)
         return idx, wgt
 
     def forward(self, x, batch):

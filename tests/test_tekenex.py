@@ -397,3 +397,39 @@ def test_long_decoding_in_bfloat16_stays_near_the_plain_choice(tmp_path, cuda_de
                for tok, row in zip(toks, logits[len(prompt) - 1:]))
     assert near >= 143, f"only {near} of 150 tokens are near the plain choice"
     assert eng.runner.cache.free_pages() == 32
+
+
+def test_command_line_and_seeded_sampling(tmp_path, cuda_device):
+    """`python -m gollmgo_b200 generate` and `bench` on a Tekenex folder; sampling with a temperature and a
+    seed gives the same tokens alone and in a batch (the logits do not depend on the batch)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from gollmgo_b200 import Engine, SamplingParams
+    cfg, page = tk.get("tek_c")
+    weights = tk.random_weights(cfg, seed=35)
+    d = tk.model_folder(tmp_path, "tek_c", cfg, weights)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, "-m", "gollmgo_b200"]
+    common = ["--model", d, "--dtype", "float32", "--block-size", str(page), "--num-blocks", "16",
+              "--max-batch-size", "4", "--max-token-budget", "64", "--log-level", "error"]
+    p = subprocess.run(base + ["generate", *common, "--prompt-ids", "5,6,7", "--prompt-ids", "9", "--max-tokens", "5",
+                               "--ignore-eos"], capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stderr
+    lines = [json.loads(l) for l in p.stdout.strip().splitlines()]
+    assert lines[0]["token_ids"] == plain_greedy(cfg, weights, [5, 6, 7], 5)
+    assert lines[1]["token_ids"] == plain_greedy(cfg, weights, [9], 5)
+    p = subprocess.run(base + ["bench", *common, "--mode", "offline", "--num-prompts", "5", "--prompt-len", "12",
+                               "--output-len", "4"], capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stderr
+    res = json.loads(p.stdout)
+    assert res["num_prompts"] == 5 and res["tokens_per_second"] > 0 and res["error_count"] == 0
+    prompts = list(tt.random_requests(cfg["vocab"], [3, 30, 11], seed=10).values())
+    params = [SamplingParams(temperature=0.9, top_k=20, seed=70 + i, max_tokens=10, ignore_eos=True) for i in range(3)]
+    eng = Engine(d, dtype="float32", block_size=page, num_blocks=16, max_batch_size=4, max_token_budget=48,
+                 prefill_chunk_size=16)
+    together = [o.token_ids for o in eng.generate(prompts, params)]
+    alone = [eng.generate([pr], [pa])[0].token_ids for pr, pa in zip(prompts, params)]
+    assert together == alone
+    assert eng.runner.cache.free_pages() == 16
