@@ -21,9 +21,11 @@
 // gg_gemm_tc_grouped).
 #include <mma.h>
 
+#include <stdlib.h>
+
 #include <type_traits>
 
-#include "common.cuh"
+#include "attention_common.cuh"
 
 #define GGM_BM 32
 #define GGM_BN 64
@@ -213,6 +215,138 @@ __global__ void __launch_bounds__(GGM_THREADS, (sizeof(TA) == 2 ? (GATED ? 2 : 4
   }
 }
 
+// The same product for bfloat16 with long K (the experts' products of decoded tokens, where a CTA
+// streams its slab of W and the rows are few): K in steps of 64 through a ring of four shared-memory
+// stages filled by cp.async, so that three steps of a CTA are in flight while it multiplies the
+// fourth; two CTAs per SM.  Rows past a group's end and columns past N or K arrive as zeros
+// (cp.async with a source size of 0).  Needs what VEC needs.
+#define GGR_BK 64
+#define GGR_LD (GGR_BK + 8)
+#define GGR_STAGES 4
+
+template <bool GATED>
+__global__ void __launch_bounds__(GGM_THREADS, 2) grouped_gemm_ring_kernel(GroupedArgs a) {
+  using TA = __nv_bfloat16;
+  constexpr int NB = GATED ? 2 : 1;
+  constexpr int CPR = GGR_BK / 8;                                // 16-byte chunks in a tile row
+  constexpr int A_ELEMS = GGM_BM * GGR_LD, B_ELEMS = GGM_BN * GGR_LD;
+  constexpr int STAGE_ELEMS = A_ELEMS + NB * B_ELEMS;
+  extern __shared__ __align__(128) unsigned char ring_raw[];
+  __shared__ int arow_s[GGM_BM];
+  TA* stages = reinterpret_cast<TA*>(ring_raw);
+  float* Cs = reinterpret_cast<float*>(ring_raw);                // over the ring once it has drained
+  pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  int g = -1, r0 = 0, r_end = 0;
+  if (a.offsets) {
+    int tile = blockIdx.y;
+    for (int e = 0; e < a.G; ++e) {
+      const int lo = a.offsets[e], hi = a.offsets[e + 1];
+      const int nt = (hi - lo + GGM_BM - 1) / GGM_BM;
+      if (tile < nt) { g = e; r0 = lo + tile * GGM_BM; r_end = hi; break; }
+      tile -= nt;
+    }
+    if (g < 0) return;
+  } else {
+    g = blockIdx.z; r0 = blockIdx.y * GGM_BM; r_end = a.M;
+    if (r0 >= r_end) return;
+  }
+  const int n0 = blockIdx.x * GGM_BN;
+  const int nrows = min(GGM_BM, r_end - r0);
+  if (tid < GGM_BM) arow_s[tid] = tid < nrows ? (a.row_index ? a.row_index[r0 + tid] / a.row_div : r0 + tid) : -1;
+  __syncthreads();
+  const int N = a.N, K = a.K;
+  const TA* A = (const TA*)a.A + (size_t)g * a.a_group_cols;
+  const TA* W = (const TA*)a.W + (size_t)g * NB * N * K;
+
+  // what this thread fetches in every step: one chunk of A, two of each W tile
+  const int ar = tid / CPR, ac = (tid % CPR) * 8;
+  const int arow = arow_s[ar];
+  const TA* a_src = A + (size_t)(arow >= 0 ? arow : 0) * a.lda + ac;
+  const TA* b_src[2];
+  bool b_ok[2];
+  int b_off[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int e = tid + u * GGM_THREADS, n = e / CPR, c = (e % CPR) * 8;
+    b_ok[u] = n0 + n < N;
+    b_src[u] = W + (size_t)(b_ok[u] ? n0 + n : 0) * K + c;
+    b_off[u] = n * GGR_LD + c;
+  }
+  auto issue = [&](int stage, int k0) {
+    TA* As = stages + stage * STAGE_ELEMS;
+    TA* Bs = As + A_ELEMS;
+    const bool kin = k0 + ac < K;
+    cp_async16(smem_u32(As + ar * GGR_LD + ac), kin ? a_src + k0 : A, (arow >= 0 && kin) ? 16 : 0);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int c = (tid + u * GGM_THREADS) % CPR * 8;
+      const bool ok = b_ok[u] && k0 + c < K;
+      cp_async16(smem_u32(Bs + b_off[u]), ok ? b_src[u] + k0 : W, ok ? 16 : 0);
+      if (GATED) cp_async16(smem_u32(Bs + B_ELEMS + b_off[u]), ok ? b_src[u] + (size_t)N * K + k0 : W, ok ? 16 : 0);
+    }
+  };
+
+  const int warp = tid >> 5, rt = warp >> 2, ct = warp & 3;
+  nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float> acc0, acc1;
+  nvcuda::wmma::fill_fragment(acc0, 0.f);
+  nvcuda::wmma::fill_fragment(acc1, 0.f);
+  const int nk = (K + GGR_BK - 1) / GGR_BK;
+#pragma unroll
+  for (int s = 0; s < GGR_STAGES - 1; ++s) {
+    if (s < nk) issue(s, s * GGR_BK);
+    cp_async_commit();
+  }
+  for (int it = 0; it < nk; ++it) {
+    cp_async_wait<GGR_STAGES - 2>();                             // this step's stage has landed
+    __syncthreads();                                             // ... for every thread; and the stage refilled below is used up
+    const int nxt = it + GGR_STAGES - 1;
+    if (nxt < nk) issue(nxt % GGR_STAGES, nxt * GGR_BK);
+    cp_async_commit();
+    const TA* As = stages + (it % GGR_STAGES) * STAGE_ELEMS;
+    const TA* Bs = As + A_ELEMS;
+    using namespace nvcuda;
+    wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+    wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+#pragma unroll
+    for (int kk = 0; kk < GGR_BK; kk += 16) {
+      wmma::load_matrix_sync(fa, As + rt * 16 * GGR_LD + kk, GGR_LD);
+      wmma::load_matrix_sync(fb, Bs + ct * 16 * GGR_LD + kk, GGR_LD);
+      wmma::mma_sync(acc0, fa, fb, acc0);
+      if (GATED) {
+        wmma::load_matrix_sync(fb, Bs + B_ELEMS + ct * 16 * GGR_LD + kk, GGR_LD);
+        wmma::mma_sync(acc1, fa, fb, acc1);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  float* Cs1 = Cs + (NB - 1) * GGM_BM * GGM_LDC;
+  nvcuda::wmma::store_matrix_sync(Cs + rt * 16 * GGM_LDC + ct * 16, acc0, GGM_LDC, nvcuda::wmma::mem_row_major);
+  if (GATED) nvcuda::wmma::store_matrix_sync(Cs1 + rt * 16 * GGM_LDC + ct * 16, acc1, GGM_LDC, nvcuda::wmma::mem_row_major);
+  __syncthreads();
+  TA* out = (TA*)a.out + (size_t)g * a.o_group_cols;
+  for (int e = tid; e < GGM_BM * GGM_BN; e += GGM_THREADS) {
+    const int r = e / GGM_BN, c = e - r * GGM_BN;
+    const int col = n0 + c;
+    if (r >= nrows || col >= a.Np) continue;
+    float v = 0.f;
+    if (col < N) {
+      v = Cs[r * GGM_LDC + c];
+      if (GATED) {
+        const float u = Cs1[r * GGM_LDC + c];
+        v = v / (1.f + expf(-v)) * u;
+      }
+      if (a.gate) {
+        const float z = to_f32(((const TA*)a.gate)[(size_t)arow_s[r] * a.ldg + a.gate_col0 + g]);
+        v *= 1.f / (1.f + expf(-z));
+      }
+    }
+    out[(size_t)(r0 + r) * a.ldo + col] = from_f32<TA>(v);
+  }
+}
+
 extern "C" int gg_grouped_gemm(const void* A, long long lda, long long a_group_cols, const int* row_index,
                                int row_div, const void* W, void* out, long long ldo, long long o_group_cols,
                                const int* offsets, int M, int G, int N, int K, int Np, int gated,
@@ -239,6 +373,16 @@ extern "C" int gg_grouped_gemm(const void* A, long long lda, long long a_group_c
     else if (vec) gg_launch(grouped_gemm_kernel<T, false, BK, true>, grid, dim3(GGM_THREADS), 0, stream, a);           \
     else gg_launch(grouped_gemm_kernel<T, false, BK, false>, grid, dim3(GGM_THREADS), 0, stream, a);                   \
   } while (0)
+  static const bool ring_on = !(getenv("GOLLMGO_B200_GROUPED_RING") && getenv("GOLLMGO_B200_GROUPED_RING")[0] == '0');
+  if (act_dtype == GG_BF16 && vec && K >= 4 * GGR_BK && ring_on) {
+    const size_t smem = (size_t)GGR_STAGES * (GGM_BM + (gated ? 2 : 1) * GGM_BN) * GGR_LD * sizeof(__nv_bfloat16);
+    cudaError_t e = gated ? cudaFuncSetAttribute(grouped_gemm_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                          : cudaFuncSetAttribute(grouped_gemm_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "grouped_gemm: %s", cudaGetErrorString(e));
+    if (gated) gg_launch(grouped_gemm_ring_kernel<true>, grid, dim3(GGM_THREADS), smem, stream, a);
+    else gg_launch(grouped_gemm_ring_kernel<false>, grid, dim3(GGM_THREADS), smem, stream, a);
+    return gg_check_launch("grouped_gemm");
+  }
   if (act_dtype == GG_F32) {
     GGM_LAUNCH(float, 32);
   } else if (act_dtype == GG_BF16) {

@@ -124,13 +124,14 @@ def test_router(kit, dtype, experts, top):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("experts,top,shared,T", [(6, 2, 24, 37), (4, 1, 0, 5), (3, 3, 40, 1), (12, 2, 16, 150),
-                                                  (6, 2, 24, 700), (20, 3, 0, 400)])
-def test_mixture_of_experts(kit, dtype, experts, top, shared, T):
-    """Few rows (the kernel that streams the chosen experts' weights) and many rows (in bfloat16 the
-    tcgen05 product over rows gathered into whole tiles per expert, some experts with no row at all)."""
+@pytest.mark.parametrize("experts,top,shared,T,D,F", [(6, 2, 24, 37, 40, 24), (4, 1, 0, 5, 40, 24), (3, 3, 40, 1, 40, 24),
+                                                      (12, 2, 16, 150, 40, 24), (6, 2, 24, 700, 40, 24), (20, 3, 0, 400, 40, 24),
+                                                      (6, 2, 72, 9, 320, 264), (5, 2, 0, 70, 264, 328)])
+def test_mixture_of_experts(kit, dtype, experts, top, shared, T, D, F):
+    """Few rows (the kernels that stream the chosen experts' weights: K in one or two steps, and, from
+    256 values of K, through a ring of cp.async stages with a ragged last step) and many rows (in bfloat16
+    the tcgen05 product over rows gathered into whole tiles per expert, some experts with no row at all)."""
     torch.manual_seed(4)
-    D, F = 40, 24
     sh = kit.parts.PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": shared, "names": ("gate", "up", "down")}) \
         if shared else None
     moe = kit.parts.build_feed_forward(kit.parts.PartSpec("moe", {"hidden_size": D, "intermediate_size": F, "experts": experts,
