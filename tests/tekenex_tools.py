@@ -42,9 +42,14 @@ TEK_C = {"architecture": "Tekenex", "vocab": 257, "width": 96, "norm": {"eps": 3
     _layer(18, 8, 12, 128, 0.4, _dense(96)),
     _layer(18, 8, 12, 128, 0.4, _moe(3, 3, 48, 80)),
 ]}
+# sizes that are no multiple of 8: no kernel may count on 16-byte rows
+TEK_D = {"architecture": "Tekenex", "vocab": 150, "width": 100, "norm": {"eps": 2e-6}, "layers": [
+    _layer(2, 12, 20, 28, 0.3, _moe(3, 2, 20, 28)),
+    _layer(5, 6, 10, 28, 0.45, _dense(52)),
+]}
 
 # name -> (config, page size)
-TINY = {"tek_a": (TEK_A, 16), "tek_b": (TEK_B, 8), "tek_c": (TEK_C, 32)}
+TINY = {"tek_a": (TEK_A, 16), "tek_b": (TEK_B, 8), "tek_c": (TEK_C, 32), "tek_d": (TEK_D, 16)}
 
 
 def get(name):

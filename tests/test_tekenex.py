@@ -283,7 +283,8 @@ def test_latent_cache_keeps_one_row_per_token(kit):
 
 
 # ------------------------------------------------------------------ whole models through bin/trace_run
-LENGTHS = {"tek_a": [1, 5, 37, 70, 130, 96], "tek_b": [2, 64, 65, 131, 300, 33], "tek_c": [3, 66, 40, 150, 97, 129]}
+LENGTHS = {"tek_a": [1, 5, 37, 70, 130, 96], "tek_b": [2, 64, 65, 131, 300, 33], "tek_c": [3, 66, 40, 150, 97, 129],
+           "tek_d": [4, 17, 80, 33, 65, 120]}
 # float32: every row to a few units of rounding.  bfloat16: these models are narrow and deep enough in norms that
 # a row's error varies widely with its content, so nine rows in ten must be within 4 % of the row's largest logit and
 # none further off than what a lost or foreign key would cause (such a row is off by its whole size).
@@ -317,7 +318,7 @@ def plain_logits(cfg, weights, requests):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tek_a", "tek_b", "tek_c"])
+@pytest.mark.parametrize("name", ["tek_a", "tek_b", "tek_c", "tek_d"])
 def test_replay_matches_plain(tmp_path, cuda_device, name, dtype):
     cfg, page = tk.get(name)
     weights = tk.random_weights(cfg, seed=31)

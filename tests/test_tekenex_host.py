@@ -27,7 +27,7 @@ def test_registry_finds_the_design_by_its_singular_key():
     assert spec.layers[1].feed_forward.kind == "moe" and spec.layers[0].feed_forward.kind == "mlp"
 
 
-@pytest.mark.parametrize("name", ["tek_a", "tek_b", "tek_c"])
+@pytest.mark.parametrize("name", ["tek_a", "tek_b", "tek_c", "tek_d"])
 def test_manifest_is_the_designs_tensor_list(name):
     from gollmgo_b200.parts import manifest_for_config
     cfg, _ = tk.get(name)
