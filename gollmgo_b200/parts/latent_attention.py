@@ -51,8 +51,14 @@ class LatentAttention:
         self.gated = bool(spec.get("gate", True))
         self.names = {**DEFAULT_NAMES, **(spec.get("names") or {})}
         self.rank_p = -(-self.rank // RANK_ALIGN) * RANK_ALIGN
-        if self.rank_p > 256:
-            raise ValueError(f"a latent of {self.rank} values is beyond what the attention kernels take as a head (256)")
+        # A latent wider than the attention kernels' head size (256) cannot be read as a head: such a layer
+        # caches the expanded keys and values instead (heads x max(dim, vdim) values each, zero-padded to one
+        # size) and runs as ordinary multi-head attention.  More cache, the same result.
+        self.expanded = self.rank_p > 256
+        self.dmax = -(-max(self.dim, self.vdim) // 8) * 8
+        if self.expanded and self.dmax > 256:
+            raise ValueError(f"a latent of {self.rank} values with heads of {self.dim} / {self.vdim} values is beyond "
+                             f"what the attention kernels take (256 for the latent or for the heads)")
         # columns of the stacked first product: q | latent | gates, each start a multiple of 8
         a8 = lambda n: -(-n // 8) * 8
         self.col_c = a8(self.nh * self.dim)
@@ -66,30 +72,39 @@ class LatentAttention:
         ws.reserve("lat_o", T * self.nh * self.rank_p, ctx.act_dtype)
         ws.reserve("attn_out", T * self.nh * self.vdim, ctx.act_dtype)
         ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
-        self._ctas_per_split = -(-self.nh // 16)
+        # the attention as the kernels see it: kv heads, query heads per kv head, head size
+        self._nkv, self._group, self._d = (self.nh, 1, self.dmax) if self.expanded else (1, self.nh, self.rank_p)
+        self._ctas_per_split = self._nkv * -(-self._group // 16)
         self._cluster_cap = None
         if ctx.device.type == "cuda":
-            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.rank_p, s, self.nh)
+            self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self._d, s, self._group)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
         esize = torch.empty((), dtype=ctx.act_dtype).element_size()
-        self._tile_bytes = TILE_KEYS * self.rank_p * esize
+        self._tile_bytes = TILE_KEYS * self._d * esize * (2 if self.expanded else 1)
         rows = max(n * self._splits(n, TILE_KEYS << b) for n in range(1, ctx.max_seqs + 1)
                    for b in range(MAX_TILES.bit_length()))
-        ws.reserve("attn_part_o", rows * self.nh * self.rank_p, torch.float32)
+        ws.reserve("attn_part_o", rows * self.nh * self._d, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
+        if self.expanded:
+            ws.reserve("lat_c", T * self.rank_p, ctx.act_dtype)
+            ws.reserve("lat_qkv", T * 3 * self.nh * self.dmax, ctx.act_dtype)
+            ws.reserve("lat_o", T * self.nh * self.dmax, ctx.act_dtype)
+            self._iota = torch.arange(T, dtype=torch.int32, device=ctx.device)
         self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = None
 
     def cache_need(self):
+        if self.expanded:
+            return PagedKVNeed(self.nh, self.dmax, None)
         return PagedKVNeed(1, self.rank_p, None, shared_kv=True)
 
     def _fast(self):
-        return self.ctx.act_dtype == torch.bfloat16 and self.rank_p in (64, 128) and ATTN_POLICY != "general"
+        return self.ctx.act_dtype == torch.bfloat16 and self._d in (64, 128) and ATTN_POLICY != "general"
 
     def query_tiles(self):
         need = [TILES_GENERAL]
         if self._fast():
             need.append(TILES_MMA)
-            if ATTN_POLICY == "auto" and self.nh % 2 == 0:
+            if ATTN_POLICY == "auto" and (self._group % 2 == 0 or self._group == 1):
                 need.append(TILES_TC)
         return need
 
@@ -127,9 +142,64 @@ class LatentAttention:
         # to the latent's space with the same grouped product that brings the result back
         self.w_uk_t = get(n["uk"]).view(self.nh, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = get(n["uv"]).view(self.nh, self.vdim, self.rank).contiguous()
+        self.w_uk = get(n["uk"]).view(self.nh, self.dim, self.rank).contiguous() if self.expanded else None
         self.w_o = get(n["o"]).contiguous()
 
+    def _attend(self, q, q_stride, kc, vc, group, batch, o):
+        """The engine's paged attention over this step's queries q (head h of token t at q[t, h * d ...])."""
+        ws, nh, nkv, d, ps = self.ctx.workspace, self.nh, self._nkv, self._d, self.ctx.page_size
+        bt = batch.block_tables[group]
+        if batch.num_portions:
+            if TILES_GENERAL not in batch.tiles:
+                raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
+                                   "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
+            t16, t64, t128 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA), batch.tiles.get(TILES_TC)
+            if not self._fast():
+                t64 = t128 = None
+            ops.attn_prefill(q, q_stride, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                             t16.seq, t16.q0, t16.count, o, nh, nkv, d, ps, 0, self.scale,
+                             t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
+                             allow_mma=t64 is not None,
+                             tile128_seq=t128.seq if t128 else None, tile128_q0=t128.q0 if t128 else None,
+                             num_tiles128=t128.count if t128 else 0, allow_tc=t128 is not None)
+        if batch.num_decode:
+            n = batch.num_decode
+            facts = getattr(batch, "facts", None)
+            longest = facts.max_context if facts is not None else max(s + l for s, l in zip(batch.q_starts, batch.q_lens))
+            splits = self._splits(n, longest)
+            ops.attn_decode(q, q_stride, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                            batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * nh * splits * d),
+                            ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, nkv, d, ps, 0, self.scale,
+                            allow_mma=self._fast())
+
+    def _forward_expanded(self, x, batch, cache, writes_cache):
+        """Keys and values expanded from the latent before they are cached (a latent too wide to be a head)."""
+        T, ws = x.shape[0], self.ctx.workspace
+        kc, vc, group = cache
+        nh, R, Rp, dm = self.nh, self.rank, self.rank_p, self.dmax
+        proj = ws.get("lat_proj", T, self.width1)
+        linear(x, self.w_in, proj)
+        c = ws.get("lat_c", T, Rp)
+        ops.latent_norm_write(proj, self.col_c, R, self.w_norm, self.eps, self._iota[:T], c)      # row t of c: the latent of token t
+        qkv = ws.get("lat_qkv", T, 3 * nh * dm)
+        qkv.zero_()                                           # the padding of every head stays zero
+        qkv.view(T, 3, nh, dm)[:, 0, :, :self.dim].copy_(proj[:, :nh * self.dim].view(T, nh, self.dim))
+        ops.grouped_gemm(c, self.w_uk, qkv[:, nh * dm:], self.dim, R, nh, a_group_cols=0, o_group_cols=dm, n_padded=dm, rows=T)
+        ops.grouped_gemm(c, self.w_uv, qkv[:, 2 * nh * dm:], self.vdim, R, nh, a_group_cols=0, o_group_cols=dm, n_padded=dm, rows=T)
+        ops.rope_kv_write(qkv, batch.positions, batch.slot_mapping[group], None, kc, vc, nh, nh, dm, self.ctx.page_size,
+                          False, writes_cache)
+        o = ws.get("lat_o", T, nh * dm)
+        self._attend(qkv, 3 * nh * dm, kc, vc, group, batch, o)
+        a = ws.get("attn_out", T, nh * self.vdim)
+        a3 = a.view(T, nh, self.vdim)
+        a3.copy_(o.view(T, nh, dm)[:, :, :self.vdim])
+        if self.gated:
+            ops.head_gate(a, proj, self.col_g, nh)
+        return linear(a, self.w_o, ws.get("mixer_out", T, self.hidden))
+
     def forward(self, x, batch, cache, writes_cache=True):
+        if self.expanded:
+            return self._forward_expanded(x, batch, cache, writes_cache)
         T, ws = x.shape[0], self.ctx.workspace
         kc, vc, group = cache
         nh, R, Rp = self.nh, self.rank, self.rank_p
@@ -147,31 +217,7 @@ class LatentAttention:
             ops.grouped_gemm(proj, self.w_uk_t, q, R, self.dim, nh, a_group_cols=self.dim, o_group_cols=Rp,
                              n_padded=Rp, rows=T)
         o = ws.get("lat_o", T, nh * Rp)
-        bt = batch.block_tables[group]
-        ps = self.ctx.page_size
-        if batch.num_portions:
-            if TILES_GENERAL not in batch.tiles:
-                raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
-                                   "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
-            t16, t64, t128 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA), batch.tiles.get(TILES_TC)
-            fast = self._fast()
-            if not fast:
-                t64 = t128 = None
-            ops.attn_prefill(q, nh * Rp, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
-                             t16.seq, t16.q0, t16.count, o, nh, 1, Rp, ps, 0, self.scale,
-                             t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
-                             allow_mma=t64 is not None,
-                             tile128_seq=t128.seq if t128 else None, tile128_q0=t128.q0 if t128 else None,
-                             num_tiles128=t128.count if t128 else 0, allow_tc=t128 is not None)
-        if batch.num_decode:
-            n = batch.num_decode
-            facts = getattr(batch, "facts", None)
-            longest = facts.max_context if facts is not None else max(s + l for s, l in zip(batch.q_starts, batch.q_lens))
-            splits = self._splits(n, longest)
-            ops.attn_decode(q, nh * Rp, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
-                            batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * nh * splits * Rp),
-                            ws.get("attn_part_ml", 1, n * nh * splits * 2), o, nh, 1, Rp, ps, 0, self.scale,
-                            allow_mma=self._fast())
+        self._attend(q, nh * Rp, kc, vc, group, batch, o)
         a = ws.get("attn_out", T, nh * self.vdim)
         if lib:
             torch.bmm(o.view(T, nh, Rp).transpose(0, 1), self.w_uv.transpose(1, 2), out=a.view(T, nh, self.vdim).transpose(0, 1))

@@ -42,10 +42,11 @@ TEK_C = {"architecture": "Tekenex", "vocab": 257, "width": 96, "norm": {"eps": 3
     _layer(18, 8, 12, 128, 0.4, _dense(96)),
     _layer(18, 8, 12, 128, 0.4, _moe(3, 3, 48, 80)),
 ]}
-# sizes that are no multiple of 8: no kernel may count on 16-byte rows
+# sizes that are no multiple of 8: no kernel may count on 16-byte rows; the second layer's latent is wider than
+# an attention head can be, so that layer caches expanded keys and values (a second cache group)
 TEK_D = {"architecture": "Tekenex", "vocab": 150, "width": 100, "norm": {"eps": 2e-6}, "layers": [
     _layer(2, 12, 20, 28, 0.3, _moe(3, 2, 20, 28)),
-    _layer(5, 6, 10, 28, 0.45, _dense(52)),
+    _layer(5, 6, 10, 260, 0.45, _dense(52)),
 ]}
 
 # name -> (config, page size)

@@ -224,12 +224,13 @@ def tagged_weights(D, H, d, v, r, scale, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(64, 3, 16, 24, 40, 16), (96, 4, 32, 32, 64, 8), (128, 18, 8, 12, 128, 32),
-                                   (80, 2, 24, 8, 200, 16)])
+                                   (80, 2, 24, 8, 200, 16), (96, 2, 16, 40, 300, 16), (96, 2, 64, 48, 264, 8)])
 def test_latent_attention_finds_one_key_among_hundreds(kit, dtype, shape):
     """Queries made to pick out single keys: the very first tokens, keys at both sides of page
     borders, keys hundreds of tokens back, a key that was itself decoded; asked for from prompt
     portions of several sizes (down to two tokens) and from single decoded tokens.  A kernel that
-    loses one of these keys returns another token's values."""
+    loses one of these keys returns another token's values.  The last two shapes have latents wider
+    than an attention head can be: the layer then caches expanded keys and values."""
     D, H, d, v, r, page = shape
     scale, eps = 1.3 / math.sqrt(d), 1e-6
     mixer, _, _ = make_mixer(kit, dtype, D, H, d, v, r, scale, page)
@@ -273,6 +274,8 @@ def test_latent_attention_token_by_token_equals_prefill(kit, dtype):
 
 
 def test_latent_cache_keeps_one_row_per_token(kit):
+    wide, _, _ = make_mixer(kit, torch.bfloat16, 64, 3, 16, 24, 300, 0.3, 16)
+    assert wide.cache_need() == kit.parts.latent_attention.PagedKVNeed(3, 24, None)      # expanded: heads x max(dim, vdim)
     mixer, _, _ = make_mixer(kit, torch.bfloat16, 64, 3, 16, 24, 40, 0.3, 16)
     need = mixer.cache_need()
     assert need.shared_kv and need.n_kv_heads == 1 and need.head_dim == 48        # 40 padded to a multiple of 16
