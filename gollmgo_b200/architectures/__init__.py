@@ -1,2 +1,3 @@
 from . import llama     # registers "LlamaForCausalLM"
 from . import tekenex   # registers "Tekenex"
+from . import bevuvik   # registers "Bevuvik"

@@ -5,11 +5,15 @@ Layers are grouped by what they need of the cache.  A *paged* need is
 (kv heads, head size, window); layers with equal needs share one group: one page
 pool, one block table per request, one device tensor of shape
 ``[layers of the group, 2 (k, v), pages, kv heads, page size, head size]`` (one
-instead of 2 where keys and values are the same rows: ``shared_kv``), so one page
-id addresses every layer of the group.  A group with a window gives a
+instead of 2 where keys and values are the same rows: ``shared_kv``; two tensors
+where values have a head count or size of their own: ``v_heads``, ``v_head_dim``),
+so one page id addresses every layer of the group.  A group with a window gives a
 page back as soon as every token in it is behind the window of all future
 queries.  A *fixed-state* need is a tensor shape per request; its buffer is
-indexed by the request's state slot.
+indexed by the request's state slot.  A cache entry may need several things at
+once (a mixer with an attention branch and a recurrent branch): its need is then
+a tuple of needs, part j of entry i is addressed as ``(i, j)``, and the entry's
+view of the cache is the tuple of its parts' views.
 
 Reference: internal/kvcache/block_pool.go, block_table.go (one group, no window,
 no state), kernels/gollmgo_kvcache.cu:11-63 (device layout [layer][slot][head][d]).
@@ -32,6 +36,12 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None      # None: all keys are kept
     shared_kv: bool = False           # keys and values are one tensor (a latent both are expanded from)
+    v_heads: Optional[int] = None     # value heads and their size where they differ from the keys'
+    v_head_dim: Optional[int] = None  # (None: as the keys); values then live in a tensor of their own
+
+    @property
+    def split_kv(self) -> bool:
+        return (self.v_heads or self.n_kv_heads) != self.n_kv_heads or (self.v_head_dim or self.head_dim) != self.head_dim
 
 
 @dataclass(frozen=True)
@@ -46,6 +56,7 @@ class PagedGroup:
     cache_ids: List[int]              # which cache entries (run-order caches) live here
     pool: PagePool
     kv: object = None                 # device tensor [n, 2, pages, nkv, page, d] or None on the host
+    v: object = None                  # values [n, 1, pages, v heads, page, dv] where their shape differs (kv then holds keys only)
 
 
 @dataclass
@@ -80,7 +91,17 @@ class CacheManager:
         self.poison_freed = os.environ.get("GOLLMGO_B200_POISON_FREED", "0") == "1"
         self.tab: List[np.ndarray] = []
         self.ntok = np.zeros(max_requests, dtype=np.int32)
+        flat = []
+
+        def spread(key, need):                 # part j of entry i is (i, j), part k of that ((i, j), k)
+            if isinstance(need, (tuple, list)):
+                for j, sub in enumerate(need):
+                    spread((key, j), sub)
+            else:
+                flat.append((key, need))
         for cid, need in enumerate(needs):
+            spread(cid, need)
+        for cid, need in flat:
             if need is None:
                 continue
             if isinstance(need, PagedKVNeed):
@@ -101,8 +122,12 @@ class CacheManager:
         if device is not None:
             import torch
             for g in self.groups:
-                g.kv = torch.zeros(len(g.cache_ids), 1 if g.need.shared_kv else 2, num_pages, g.need.n_kv_heads,
-                                   page_size, g.need.head_dim, dtype=dtype, device=device)
+                split = g.need.split_kv
+                g.kv = torch.zeros(len(g.cache_ids), 1 if (g.need.shared_kv or split) else 2, num_pages,
+                                   g.need.n_kv_heads, page_size, g.need.head_dim, dtype=dtype, device=device)
+                if split:
+                    g.v = torch.zeros(len(g.cache_ids), 1, num_pages, g.need.v_heads or g.need.n_kv_heads, page_size,
+                                      g.need.v_head_dim or g.need.head_dim, dtype=dtype, device=device)
             for cid, need in self.state_needs.items():
                 self.state_buffers[cid] = torch.zeros(max_requests, *need.shape,
                                                       dtype=getattr(torch, need.dtype), device=device)
@@ -113,17 +138,43 @@ class CacheManager:
         """Bytes one page id costs over all groups (each group has its own pool of
         ``num_pages``, so this is the cost of adding one page to every pool)."""
         total = 0
-        for need in needs:
-            if isinstance(need, PagedKVNeed):
+        flat = []
+
+        def spread(need):
+            if isinstance(need, (tuple, list)):
+                for sub in need:
+                    spread(sub)
+            else:
+                flat.append(need)
+        spread(list(needs))
+        for need in flat:
+            if isinstance(need, PagedKVNeed) and need.split_kv:
+                total += (need.n_kv_heads * need.head_dim + (need.v_heads or need.n_kv_heads)
+                          * (need.v_head_dim or need.head_dim)) * page_size * element_size
+            elif isinstance(need, PagedKVNeed):
                 total += (1 if need.shared_kv else 2) * need.n_kv_heads * need.head_dim * page_size * element_size
         return total
 
-    def layer_cache(self, cache_id: int):
-        """(k, v) tensors [pages, nkv, page, d] of one cache entry, and its group index.  A group
-        whose keys and values are one tensor gives that tensor twice."""
+    def layer_cache(self, cache_id):
+        """(k, v) tensors [pages, nkv, page, d] of one cache entry (or part of one: ``(entry, part)``),
+        and its group index.  A group whose keys and values are one tensor gives that tensor twice;
+        one whose values have a shape of their own gives v as [pages, v heads, page, dv]."""
         gi, idx = self.group_of[cache_id]
         g = self.groups[gi]
+        if g.v is not None:
+            return g.kv[idx, 0], g.v[idx, 0], gi
         return g.kv[idx, 0], g.kv[idx, 0 if g.need.shared_kv else 1], gi
+
+    def cache_view(self, cache_id, need):
+        """What a mixer is handed for cache entry ``cache_id`` with ``need``: (k, v, group) for pages,
+        the state buffer for fixed state, None for none, a tuple of these for a tuple of needs."""
+        if isinstance(need, (tuple, list)):
+            return tuple(self.cache_view((cache_id, j), sub) for j, sub in enumerate(need))
+        if isinstance(need, PagedKVNeed):
+            return self.layer_cache(cache_id)
+        if need is None:
+            return None
+        return self.state_buffers[cache_id]
 
     def _give_back(self, gi: int, page: int) -> None:
         """Return a page of group gi to its pool.  With GOLLMGO_B200_POISON_FREED=1 its keys and
@@ -133,6 +184,8 @@ class CacheManager:
         g = self.groups[gi]
         if self.poison_freed and g.kv is not None:
             g.kv[:, :, page] = float("nan")
+            if g.v is not None:
+                g.v[:, :, page] = float("nan")
         g.pool.release(page)
 
     # ------------------------------------------------------------------ requests

@@ -23,6 +23,8 @@ class EngineConfig:
                                            # reference (internal/scheduler/fcfs.go:130-161)
     cuda_graphs: bool = True               # capture decode-only steps
     capture_at_start: bool = True          # capture every batch bucket when the engine is built, not at first use
+    state_slots: Optional[int] = None      # requests that can be admitted at once (each holds a state slot);
+                                           # None => twice max_batch_size, at least 8
     device: int = 0
 
     def validate(self) -> None:
@@ -36,5 +38,7 @@ class EngineConfig:
             raise ValueError("max_token_budget must be positive")
         if not (0.0 < self.max_memory_fraction <= 1.0):
             raise ValueError("max_memory_fraction must be in (0, 1]")
+        if self.state_slots is not None and self.state_slots <= 0:
+            raise ValueError("state_slots must be positive")
         if self.prefill_chunk_size < 0:
             raise ValueError("prefill_chunk_size must be >= 0")

@@ -27,12 +27,13 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
                                           const int* pos_s, int kvh, const int* bt, int lo,
                                           int hi, float* smem, float* acc) {
   constexpr int NACC = ATT_BQ * DMAX / ATT_THREADS;
-  const int d = a.d, ps = a.page_size;
+  const int d = a.d, dv = a.dv > 0 ? a.dv : a.d, ps = a.page_size;
+  const int vsh = a.v_share > 1 ? a.v_share : 1, nv = a.nkv / vsh, vh = kvh / vsh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* Qs = smem;                                  // [16][d]
   float* Ks = Qs + ATT_BQ * d;                       // [64][d+1]
-  float* Vs = Ks + ATT_BK * (d + 1);                 // [64][d]
-  float* Ss = Vs + ATT_BK * d;                       // [16][64]
+  float* Vs = Ks + ATT_BK * (d + 1);                 // [64][dv]
+  float* Ss = Vs + ATT_BK * dv;                      // [16][64]
   float* m_s = Ss + ATT_BQ * ATT_BK;                 // [16]
   float* l_s = m_s + ATT_BQ;                         // [16]
   float* al_s = l_s + ATT_BQ;                        // [16]
@@ -57,12 +58,12 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
       if (tok >= lo && tok < hi) page = bt[tok / ps];
       if (page >= 0) {
         const size_t base = (((size_t)page * a.nkv + kvh) * ps + (tok % ps)) * d;
-        for (int c = lane; c < d; c += 32) {
-          Ks[j * (d + 1) + c] = to_f32(kc[base + c]);
-          Vs[j * d + c] = to_f32(vc[base + c]);
-        }
+        const size_t vbase = (((size_t)page * nv + vh) * ps + (tok % ps)) * dv;
+        for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = to_f32(kc[base + c]);
+        for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_f32(vc[vbase + c]);
       } else {
-        for (int c = lane; c < d; c += 32) { Ks[j * (d + 1) + c] = 0.f; Vs[j * d + c] = 0.f; }
+        for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = 0.f;
+        for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = 0.f;
       }
     }
     __syncthreads();
@@ -84,7 +85,9 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
         const int r = rb + 2 * i;
         const int p = pos_s[r];
         const bool ok = tok >= lo && tok < hi && tok <= p && (a.window <= 0 || tok > p - a.window);
-        Ss[r * ATT_BK + j] = ok ? s[i] * a.scale : -INFINITY;
+        float sc = s[i] * a.scale;
+        if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+        Ss[r * ATT_BK + j] = ok ? sc : -INFINITY;
       }
     }
     __syncthreads();
@@ -112,13 +115,13 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
       const int e = tid + ATT_THREADS * i;
-      if (e < ATT_BQ * d) {
-        const int r = e / d, c = e - r * d;
+      if (e < ATT_BQ * dv) {
+        const int r = e / dv, c = e - r * dv;
         float o = acc[i] * al_s[r];
         const float* pr = Ss + r * ATT_BK;
         const float* vcol = Vs + c;
 #pragma unroll 8
-        for (int j = 0; j < ATT_BK; ++j) o = fmaf(pr[j], vcol[j * d], o);
+        for (int j = 0; j < ATT_BK; ++j) o = fmaf(pr[j], vcol[j * dv], o);
         acc[i] = o;
       }
     }
@@ -126,8 +129,13 @@ __device__ __forceinline__ void attn_tile(const AttnArgs& a, int nrows, const TA
   }
 }
 
-template <int DMAX> __host__ __device__ constexpr int attn_smem_floats(int d) {
-  return ATT_BQ * d + ATT_BK * (d + 1) + ATT_BK * d + ATT_BQ * ATT_BK + 3 * ATT_BQ;
+__host__ __device__ constexpr int attn_smem_floats(int d, int dv) {
+  return ATT_BQ * d + ATT_BK * (d + 1) + ATT_BK * dv + ATT_BQ * ATT_BK + 3 * ATT_BQ;
+}
+// where the running maximum of the rows lies in the tile's shared memory (the sums follow it)
+__device__ __forceinline__ const float* attn_tile_max(const AttnArgs& a, const float* smem) {
+  const int dv = a.dv > 0 ? a.dv : a.d;
+  return smem + ATT_BQ * a.d + ATT_BK * (a.d + 1) + ATT_BK * dv + ATT_BQ * ATT_BK;
 }
 
 // ---------------------------------------------------------------- prompt portions
@@ -155,14 +163,18 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(AttnArgs a) {
   float acc[NACC];
   attn_tile<TA, DMAX>(a, nrows, qptr_s, pos_s, kvh, a.block_tables + (size_t)b * a.bt_stride, lo, last + 1, smem, acc);
   pdl_trigger();
-  const float* l_s = smem + ATT_BQ * a.d + ATT_BK * (a.d + 1) + ATT_BK * a.d + ATT_BQ * ATT_BK + ATT_BQ;
-  TA* out = (TA*)a.out;
+  const float* l_s = attn_tile_max(a, smem) + ATT_BQ;
+  const int dv = a.dv > 0 ? a.dv : a.d;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
     const int e = threadIdx.x + ATT_THREADS * i;
-    if (e < ATT_BQ * a.d) {
-      const int r = e / a.d, c = e - r * a.d;
-      if (r < nrows) out[(size_t)(t0 + q0 + r) * a.nh * a.d + (size_t)h * a.d + c] = from_f32<TA>(acc[i] / l_s[r]);
+    if (e < ATT_BQ * dv) {
+      const int r = e / dv, c = e - r * dv;
+      if (r < nrows) {
+        const size_t at = (size_t)(t0 + q0 + r) * a.nh * dv + (size_t)h * dv + c;
+        if (a.out_f32) ((float*)a.out)[at] = acc[i] / l_s[r];
+        else ((TA*)a.out)[at] = from_f32<TA>(acc[i] / l_s[r]);
+      }
     }
   }
 }
@@ -204,16 +216,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(AttnArgs a) {
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
   }
   pdl_trigger();
-  const float* m_s = smem + ATT_BQ * a.d + ATT_BK * (a.d + 1) + ATT_BK * a.d + ATT_BQ * ATT_BK;
+  const float* m_s = attn_tile_max(a, smem);
   const float* l_s = m_s + ATT_BQ;
+  const int dv = a.dv > 0 ? a.dv : a.d;
 #pragma unroll
   for (int i = 0; i < NACC; ++i) {
     const int e = threadIdx.x + ATT_THREADS * i;
-    if (e < ATT_BQ * a.d) {
-      const int r = e / a.d, c = e - r * a.d;
+    if (e < ATT_BQ * dv) {
+      const int r = e / dv, c = e - r * dv;
       if (r < nrows) {
         const size_t row = ((size_t)blockIdx.x * a.nh + kvh * G + g0 + r) * S + split;
-        a.part_o[row * a.d + c] = acc[i];
+        a.part_o[row * dv + c] = acc[i];
         if (c == 0) {
           a.part_ml[row * 2] = lo < hi ? m_s[r] : -INFINITY;
           a.part_ml[row * 2 + 1] = lo < hi ? l_s[r] : 0.f;
@@ -231,7 +244,7 @@ __global__ void attn_merge_kernel(AttnArgs a) {
   pdl_wait();
   const int b = a.dec_seqs[blockIdx.x];
   if (b < 0) return;
-  const int h = blockIdx.y, S = a.num_splits, d = a.d;
+  const int h = blockIdx.y, S = a.num_splits, d = a.dv > 0 ? a.dv : a.d;
   const int t = a.cu_q_lens[b];
   const size_t row0 = ((size_t)blockIdx.x * a.nh + h) * S;
   float M = -INFINITY;
@@ -241,14 +254,16 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     const float m = a.part_ml[(row0 + s) * 2];
     if (m != -INFINITY) L += expf(m - M) * a.part_ml[(row0 + s) * 2 + 1];
   }
-  TA* out = (TA*)a.out + (size_t)t * a.nh * d + (size_t)h * d;
+  const size_t at = (size_t)t * a.nh * d + (size_t)h * d;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < S; ++s) {
       const float m = a.part_ml[(row0 + s) * 2];
       if (m != -INFINITY) o += expf(m - M) * a.part_o[(row0 + s) * d + c];
     }
-    out[c] = from_f32<TA>(L > 0.f ? o / L : 0.f);
+    o = L > 0.f ? o / L : 0.f;
+    if (a.out_f32) ((float*)a.out)[at + c] = o;
+    else ((TA*)a.out)[at + c] = from_f32<TA>(o);
   }
 }
 
@@ -256,6 +271,8 @@ __global__ void attn_merge_kernel(AttnArgs a) {
 static int check_common(const AttnArgs& a, const char* who) {
   GG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "%s: %d heads are not a multiple of %d kv heads", who, a.nh, a.nkv);
   GG_REQUIRE(a.d > 0 && a.d <= 256, "%s: head size %d is outside 1..256", who, a.d);
+  GG_REQUIRE(a.dv >= 0 && a.dv <= 256, "%s: value head size %d is outside 1..256", who, a.dv);
+  GG_REQUIRE(a.v_share <= 1 || a.nkv % a.v_share == 0, "%s: %d key heads cannot share values %d by %d", who, a.nkv, a.v_share, a.v_share);
   GG_REQUIRE(a.page_size > 0 && a.bt_stride > 0, "%s: bad page size %d or block table width %d", who, a.page_size, a.bt_stride);
   return GG_OK;
 }
@@ -270,15 +287,16 @@ template <typename K> static int set_smem(K kernel, size_t bytes, const char* wh
 
 #define ATT_DISPATCH(KERNEL, grid, who)                                                        \
   do {                                                                                         \
-    const size_t smem = (size_t)attn_smem_floats<0>(a.d) * sizeof(float);                      \
+    const int dvv = a.dv > 0 ? a.dv : a.d;                                                     \
+    const size_t smem = (size_t)attn_smem_floats(a.d, dvv) * sizeof(float);                    \
     int rc = GG_OK;                                                                            \
     if (dtype == GG_F32) {                                                                     \
-      if (a.d <= 64) { rc = set_smem(KERNEL<float, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
-      else if (a.d <= 128) { rc = set_smem(KERNEL<float, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      if (dvv <= 64) { rc = set_smem(KERNEL<float, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else if (dvv <= 128) { rc = set_smem(KERNEL<float, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
       else { rc = set_smem(KERNEL<float, 256>, smem, who); if (rc) return rc; gg_launch(KERNEL<float, 256>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
     } else if (dtype == GG_BF16) {                                                             \
-      if (a.d <= 64) { rc = set_smem(KERNEL<__nv_bfloat16, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
-      else if (a.d <= 128) { rc = set_smem(KERNEL<__nv_bfloat16, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      if (dvv <= 64) { rc = set_smem(KERNEL<__nv_bfloat16, 64>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 64>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
+      else if (dvv <= 128) { rc = set_smem(KERNEL<__nv_bfloat16, 128>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 128>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
       else { rc = set_smem(KERNEL<__nv_bfloat16, 256>, smem, who); if (rc) return rc; gg_launch(KERNEL<__nv_bfloat16, 256>, dim3(grid), dim3(ATT_THREADS), smem, stream, a); } \
     } else {                                                                                   \
       return gg_fail(GG_ERR_INVALID, "%s: unknown dtype %d", who, dtype);                      \
@@ -303,7 +321,8 @@ int attn_decode_general(const AttnArgs& a, int dtype, int n_dec, cudaStream_t st
 
 int attn_merge_launch(const AttnArgs& a, int dtype, int n_dec, cudaStream_t stream) {
   dim3 mgrid(n_dec, a.nh);
-  const int mthreads = a.d >= 128 ? 128 : (a.d >= 64 ? 64 : 32);
+  const int md = a.dv > 0 ? a.dv : a.d;
+  const int mthreads = md >= 128 ? 128 : (md >= 64 ? 64 : 32);
   if (dtype == GG_F32) gg_launch(attn_merge_kernel<float>, dim3(mgrid), dim3(mthreads), 0, stream, a);
   else gg_launch(attn_merge_kernel<__nv_bfloat16>, dim3(mgrid), dim3(mthreads), 0, stream, a);
   return gg_check_launch("attn_merge");
@@ -456,4 +475,48 @@ extern "C" int gg_attn_decode_flat_ctas(int d) { return attn_decode_flat_ctas(d)
 extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits, int group) {
   if (!attn_mma_supported(dtype, d)) return 0;
   return attn_decode_cluster_capacity(d, splits, group);
+}
+
+// The general kernels with everything they take: keys of size d and values of size dv, `v_share`
+// consecutive key heads reading one value head (vcache [num_pages, nkv / v_share, page_size, dv]),
+// scores capped by softcap * tanh(score / softcap) where softcap > 0, the result in float32 where
+// out_f32.  Float32 arithmetic whatever the cache's type.  part_o float[n_dec * nh * num_splits * dv].
+extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* kcache, const void* vcache,
+                                 int dtype, const int* block_tables, int bt_stride, const int* cu_q_lens,
+                                 const int* context_lens, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                 void* out, int out_f32, int nh, int nkv, int d, int dv, int v_share,
+                                 int page_size, int window, float scale, float softcap, cudaStream_t stream) {
+  AttnArgs a = {};
+  a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
+  a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
+  a.context_lens = context_lens; a.out = out; a.nh = nh; a.nkv = nkv; a.d = d;
+  a.page_size = page_size; a.window = window; a.scale = scale;
+  a.dv = dv; a.v_share = v_share; a.softcap = softcap; a.out_f32 = out_f32;
+  a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
+  int rc = check_common(a, "attn_prefill_x");
+  if (rc) return rc;
+  return attn_prefill_general(a, dtype, num_tiles, stream);
+}
+
+extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* kcache, const void* vcache,
+                                int dtype, const int* block_tables, int bt_stride, const int* cu_q_lens,
+                                const int* context_lens, const int* dec_seqs, int n_dec, int num_splits,
+                                float* part_o, float* part_ml, void* out, int out_f32, int nh, int nkv, int d,
+                                int dv, int v_share, int page_size, int window, float scale, float softcap,
+                                cudaStream_t stream) {
+  AttnArgs a = {};
+  a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
+  a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
+  a.context_lens = context_lens; a.out = out; a.nh = nh; a.nkv = nkv; a.d = d;
+  a.page_size = page_size; a.window = window; a.scale = scale;
+  a.dv = dv; a.v_share = v_share; a.softcap = softcap; a.out_f32 = out_f32;
+  a.dec_seqs = dec_seqs; a.num_splits = num_splits; a.part_o = part_o; a.part_ml = part_ml;
+  int rc = check_common(a, "attn_decode_x");
+  if (rc) return rc;
+  GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_x: bad n_dec %d or splits %d", n_dec, num_splits);
+  GG_REQUIRE(part_o && part_ml, "attn_decode_x: no scratch given");
+  if (n_dec == 0) return GG_OK;
+  rc = attn_decode_general(a, dtype, n_dec, stream);
+  if (rc) return rc;
+  return attn_merge_launch(a, dtype, n_dec, stream);
 }

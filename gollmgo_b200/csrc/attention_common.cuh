@@ -29,6 +29,11 @@ struct AttnArgs {
   const int* rope_positions;     // [T]
   const int* slot_mapping;       // [T] page * page_size + offset, < 0: no write
   int rope_write_cache;
+  // the general kernels only (attention.cu); zero = the plain case
+  int dv;                   // size of a value head where it differs from d (0: d); vcache is [num_pages, nkv / v_share, page_size, dv]
+  int v_share;              // this many consecutive key heads read one value head (0 or 1: each its own)
+  float softcap;            // > 0: score <- softcap * tanh(score / softcap) after the scaling
+  int out_f32;              // out is float32 [T, nh*dv] whatever the cache's type
 };
 
 // General kernels (attention.cu)

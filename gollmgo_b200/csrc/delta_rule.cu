@@ -1,0 +1,299 @@
+// The gated delta rule: a linear-attention layer whose state per head is a matrix S [d, dv] in
+// float32, carried from token to token in the request's state slot:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// with k, q unit vectors (q also times d^-1/2), beta in (0, 1) and the decay g in (0, 1) per
+// head and token.  q, k and v first pass a short causal convolution over time per channel and
+// SiLU; the last taps - 1 inputs of every channel are state too.
+//
+// Three kernels a step, every one for any mix of prompt portions and single decoded tokens:
+//   delta_prep     per (token, head unit): convolution + SiLU, unit norms, beta and decay
+//   delta_recur    per (sequence, head, 32 value columns): the recurrence over the portion
+//   delta_out      per (token, head): o / rms(o) * weight * silu(gate)
+// and delta_conv_state, which moves the convolution's window on after delta_prep has read it.
+// Every column j of S evolves on its own (S[:, j] only ever meets v_j and u_j), so the columns
+// of a head are spread over CTAs; four lanes share a column and split its d rows.
+// Everything here is float32 arithmetic; only the projections that come in (x, gate) and the
+// result that goes out are in the activation type.
+#include "common.cuh"
+
+// Index of the sequence that token t belongs to: the largest b with cu[b] <= t.
+__device__ __forceinline__ int seq_of_token(const int* __restrict__ cu, int B, int t) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------- convolution, norms, gates
+// grid (T, G + G + H + 1), the last unit of a token computes beta and the decay.
+// x [T, x_stride]: columns [q: G*d | k: G*d | v: H*dv]; conv_w [C, taps]; conv_state
+// [slots, taps-1, C] holds the inputs at positions start-(taps-1) .. start-1 of the sequence.
+template <typename TA>
+__global__ void delta_prep_kernel(const TA* __restrict__ x, long long x_stride, const float* __restrict__ conv_w,
+                                  const float* __restrict__ conv_state, const float* __restrict__ ba,
+                                  const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                  const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
+                                  const int* __restrict__ state_slots, int B, int G, int H, int d, int dv, int taps,
+                                  float* __restrict__ qkv_out, float* __restrict__ beta, float* __restrict__ decay) {
+  extern __shared__ float ys[];          // the unit's channels + 33 for the reduction
+  pdl_trigger();
+  const int t = blockIdx.x, u = blockIdx.y;
+  const int C = 2 * G * d + H * dv;
+  const int b = seq_of_token(cu_q_lens, B, t);
+  const int t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
+  const int slot = state_slots[b];
+  const int start = context_lens[b] - qlen;            // tokens of the sequence before this step
+  pdl_wait();
+  if (u == 2 * G + H) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      const float zb = ba[(size_t)t * 2 * H + h], za = ba[(size_t)t * 2 * H + H + h];
+      beta[(size_t)t * H + h] = 1.f / (1.f + expf(-zb));
+      decay[(size_t)t * H + h] = expf(-expf(a_log[h]) * softplus_f(za + dt_bias[h]));
+    }
+    return;
+  }
+  const bool unit = u < 2 * G;                           // a q or k head: made a unit vector
+  const int dh = unit ? d : dv;
+  const int c0 = unit ? u * d : 2 * G * d + (u - 2 * G) * dv;
+  const int i = t - t0;                                  // place in the portion
+  const float* st = (slot >= 0 && start > 0) ? conv_state + (size_t)slot * (taps - 1) * C : nullptr;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < dh; e += blockDim.x) {
+    const int c = c0 + e;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int src = i - (taps - 1) + j;
+      float xv;
+      if (src >= 0) xv = to_f32(x[(size_t)(t0 + src) * x_stride + c]);
+      else xv = st ? st[(size_t)(taps - 1 + src) * C + c] : 0.f;
+      acc = fmaf(conv_w[(size_t)c * taps + j], xv, acc);
+    }
+    const float y = silu_f(acc);
+    ys[e] = y;
+    ss += y * y;
+  }
+  float f = 1.f;
+  if (unit) {
+    const float tot = block_sum(ss, ys + dh);
+    f = rsqrtf(tot + 1e-6f);
+    if (u < G) f *= rsqrtf((float)d);
+  }
+  for (int e = threadIdx.x; e < dh; e += blockDim.x) qkv_out[(size_t)t * C + c0 + e] = ys[e] * f;
+}
+
+// grid (B, ceil(C / 128)): the window of the convolution after this step's tokens.
+template <typename TA>
+__global__ void delta_conv_state_kernel(const TA* __restrict__ x, long long x_stride, float* __restrict__ conv_state,
+                                        const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
+                                        const int* __restrict__ state_slots, int C, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int slot = state_slots[b];
+  const int t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
+  if (slot < 0 || qlen <= 0 || c >= C) return;
+  const int start = context_lens[b] - qlen;
+  float* st = conv_state + (size_t)slot * (taps - 1) * C;
+  float keep[16];
+#pragma unroll
+  for (int s = 0; s < 16; ++s) {
+    if (s < taps - 1) {
+      const int src = qlen - (taps - 1) + s;
+      if (src >= 0) keep[s] = to_f32(x[(size_t)(t0 + src) * x_stride + c]);
+      else keep[s] = start > 0 ? st[(size_t)(taps - 1 + src) * C + c] : 0.f;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < 16; ++s)
+    if (s < taps - 1) st[(size_t)s * C + c] = keep[s];
+}
+
+// ---------------------------------------------------------------- the recurrence
+#define DR_COLS 32          // value columns of one CTA
+#define DR_LANES 4          // lanes that share a column
+#define DR_CHUNK 16         // tokens staged in shared memory at a time
+
+// grid (B, H, ceil(dv / 32)), 128 threads.  state [slots, H, dv, d].
+template <int DPT>
+__global__ void __launch_bounds__(DR_COLS * DR_LANES)
+delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+                   float* __restrict__ state, const int* __restrict__ cu_q_lens, const int* __restrict__ context_lens,
+                   const int* __restrict__ state_slots, int G, int H, int d, int dv, float* __restrict__ o_raw) {
+  extern __shared__ float sm[];
+  pdl_trigger();
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
+  const int tid = threadIdx.x, r = tid & (DR_LANES - 1), cl = tid >> 2, col = col0 + cl;
+  const int C = 2 * G * d + H * dv;
+  const int slot = state_slots[b];
+  const int t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
+  if (slot < 0 || qlen <= 0) return;
+  const int start = context_lens[b] - qlen;
+  const int kvh = h / (H / G);
+  const int dp = DPT * DR_LANES;                 // d rounded up to what the lanes hold
+  float* ks = sm;                                // [CHUNK][dp]
+  float* qs = ks + DR_CHUNK * dp;                // [CHUNK][dp]
+  float* vs = qs + DR_CHUNK * dp;                // [CHUNK][COLS]
+  float* bg = vs + DR_CHUNK * DR_COLS;           // [CHUNK][2]
+  float* os = bg + DR_CHUNK * 2;                 // [CHUNK][COLS]
+  const bool live = col < dv;
+  float S[DPT];
+  float* srow = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int row = r * DPT + i;
+    S[i] = (live && start > 0 && row < d) ? srow[row] : 0.f;
+  }
+  pdl_wait();
+  for (int c0 = 0; c0 < qlen; c0 += DR_CHUNK) {
+    const int n = min(DR_CHUNK, qlen - c0);
+    __syncthreads();
+    for (int e = tid; e < n * dp; e += blockDim.x) {
+      const int tt = e / dp, row = e - tt * dp;
+      const size_t base = (size_t)(t0 + c0 + tt) * C;
+      ks[e] = row < d ? qkv[base + (size_t)(G + kvh) * d + row] : 0.f;
+      qs[e] = row < d ? qkv[base + (size_t)kvh * d + row] : 0.f;
+    }
+    for (int e = tid; e < n * DR_COLS; e += blockDim.x) {
+      const int tt = e / DR_COLS, cc = e - tt * DR_COLS;
+      vs[e] = col0 + cc < dv ? qkv[(size_t)(t0 + c0 + tt) * C + 2 * G * d + (size_t)h * dv + col0 + cc] : 0.f;
+    }
+    if (tid < n) {
+      bg[tid * 2] = beta[(size_t)(t0 + c0 + tid) * H + h];
+      bg[tid * 2 + 1] = decay[(size_t)(t0 + c0 + tid) * H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n; ++tt) {
+      const float* kr = ks + tt * dp + r * DPT;
+      const float* qr = qs + tt * dp + r * DPT;
+      const float be = bg[tt * 2], g = bg[tt * 2 + 1];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) dot = fmaf(kr[i], S[i], dot);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      const float u = be * (vs[tt * DR_COLS + cl] - g * dot);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        S[i] = fmaf(kr[i], u, g * S[i]);
+        o = fmaf(qr[i], S[i], o);
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (r == 0) os[tt * DR_COLS + cl] = o;
+    }
+    __syncthreads();
+    for (int e = tid; e < n * DR_COLS; e += blockDim.x) {
+      const int tt = e / DR_COLS, cc = e - tt * DR_COLS;
+      if (col0 + cc < dv) o_raw[(size_t)(t0 + c0 + tt) * H * dv + (size_t)h * dv + col0 + cc] = os[e];
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int row = r * DPT + i;
+      if (row < d) srow[row] = S[i];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- the gated norm of the result
+// grid (T, H): out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :])
+template <typename TA>
+__global__ void delta_out_kernel(const float* __restrict__ o_raw, const TA* __restrict__ gate, long long gate_stride,
+                                 const float* __restrict__ w, float eps, int H, int dv, TA* __restrict__ out) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* o = o_raw + (size_t)t * H * dv + (size_t)h * dv;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) ss += o[c] * o[c];
+  const float f = rsqrtf(block_sum(ss, red) / (float)dv + eps);
+  const TA* gr = gate + (size_t)t * gate_stride + (size_t)h * dv;
+  TA* y = out + (size_t)t * H * dv + (size_t)h * dv;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) y[c] = from_f32<TA>(o[c] * f * w[c] * silu_f(to_f32(gr[c])));
+}
+
+// ---------------------------------------------------------------- launchers
+extern "C" int gg_delta_prep(const void* x, long long x_stride, int dtype, const float* conv_w, float* conv_state,
+                             const float* ba, const float* a_log, const float* dt_bias, const int* cu_q_lens,
+                             const int* context_lens, const int* state_slots, int T, int B, int G, int H, int d, int dv,
+                             int taps, float* qkv_out, float* beta, float* decay, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && B > 0 && G > 0 && H > 0 && H % G == 0 && d > 0 && dv > 0, "delta_prep: bad sizes T=%d B=%d G=%d H=%d d=%d dv=%d", T, B, G, H, d, dv);
+  GG_REQUIRE(taps >= 1 && taps <= 17, "delta_prep: %d taps are outside 1..17", taps);
+  const int C = 2 * G * d + H * dv;
+  GG_REQUIRE(x_stride >= C, "delta_prep: rows of %lld values hold no %d channels", x_stride, C);
+  if (T == 0) return GG_OK;
+  const int big = d > dv ? d : dv;
+  GG_REQUIRE(big <= 8192, "delta_prep: head size %d is too large", big);
+  const size_t smem = (size_t)(big + 33) * sizeof(float);
+  const int threads = big >= 256 ? 256 : (big >= 128 ? 128 : 64);
+  const dim3 grid(T, 2 * G + H + 1);
+  GG_REQUIRE(grid.y <= 65535, "delta_prep: too many heads");
+  if (dtype == GG_F32)
+    gg_launch(delta_prep_kernel<float>, grid, dim3(threads), smem, stream, (const float*)x, x_stride, conv_w, (const float*)conv_state, ba, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
+  else if (dtype == GG_BF16)
+    gg_launch(delta_prep_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (const __nv_bfloat16*)x, x_stride, conv_w, (const float*)conv_state, ba, a_log, dt_bias, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, taps, qkv_out, beta, decay);
+  else
+    return gg_fail(GG_ERR_INVALID, "delta_prep: unknown dtype %d", dtype);
+  int rc = gg_check_launch("delta_prep");
+  if (rc || taps == 1) return rc;
+  const dim3 sgrid(B, (C + 127) / 128);
+  if (dtype == GG_F32)
+    gg_launch(delta_conv_state_kernel<float>, sgrid, dim3(128), 0, stream, (const float*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
+  else
+    gg_launch(delta_conv_state_kernel<__nv_bfloat16>, sgrid, dim3(128), 0, stream, (const __nv_bfloat16*)x, x_stride, conv_state, cu_q_lens, context_lens, state_slots, C, taps);
+  return gg_check_launch("delta_conv_state");
+}
+
+template <int DPT>
+static int delta_recur_launch(const float* qkv, const float* beta, const float* decay, float* state,
+                              const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
+                              int d, int dv, float* o_raw, cudaStream_t stream) {
+  const int dp = DPT * DR_LANES;
+  const size_t smem = (size_t)(2 * DR_CHUNK * dp + 2 * DR_CHUNK * DR_COLS + 2 * DR_CHUNK) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_recur_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "delta_recur: %s", cudaGetErrorString(e));
+  }
+  const dim3 grid(B, H, (dv + DR_COLS - 1) / DR_COLS);
+  gg_launch(delta_recur_kernel<DPT>, grid, dim3(DR_COLS * DR_LANES), smem, stream, qkv, beta, decay, state, cu_q_lens,
+            context_lens, state_slots, G, H, d, dv, o_raw);
+  return gg_check_launch("delta_recur");
+}
+
+extern "C" int gg_delta_recur(const float* qkv, const float* beta, const float* decay, float* state,
+                              const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
+                              int d, int dv, float* o_raw, cudaStream_t stream) {
+  GG_REQUIRE(B > 0 && G > 0 && H > 0 && H % G == 0 && d > 0 && dv > 0, "delta_recur: bad sizes B=%d G=%d H=%d d=%d dv=%d", B, G, H, d, dv);
+  GG_REQUIRE(d <= 256, "delta_recur: key size %d is beyond 256", d);
+  GG_REQUIRE(H <= 65535 && (dv + DR_COLS - 1) / DR_COLS <= 65535, "delta_recur: too many heads or columns");
+#define DR_GO(N) return delta_recur_launch<N>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream)
+  if (d <= 16) DR_GO(4);
+  if (d <= 32) DR_GO(8);
+  if (d <= 64) DR_GO(16);
+  if (d <= 128) DR_GO(32);
+  DR_GO(64);
+#undef DR_GO
+}
+
+extern "C" int gg_delta_out(const float* o_raw, const void* gate, long long gate_stride, int dtype, const float* w,
+                            float eps, int T, int H, int dv, void* out, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && dv > 0 && H <= 65535, "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
+  if (T == 0) return GG_OK;
+  const int threads = dv >= 256 ? 256 : (dv >= 128 ? 128 : 64);
+  const dim3 grid(T, H);
+  if (dtype == GG_F32)
+    gg_launch(delta_out_kernel<float>, grid, dim3(threads), 0, stream, o_raw, (const float*)gate, gate_stride, w, eps, H, dv, (float*)out);
+  else if (dtype == GG_BF16)
+    gg_launch(delta_out_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, o_raw, (const __nv_bfloat16*)gate, gate_stride, w, eps, H, dv, (__nv_bfloat16*)out);
+  else
+    return gg_fail(GG_ERR_INVALID, "delta_out: unknown dtype %d", dtype);
+  return gg_check_launch("delta_out");
+}

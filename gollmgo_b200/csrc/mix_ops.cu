@@ -1,0 +1,183 @@
+// Small per-row kernels that join the branches of a layer: the weighted sum of RMS-normed
+// branch outputs, the scaled add of sublayer outputs to the residual stream, a bias on rows,
+// the rounded concatenation of two float32 streams, a clamped gated activation, and the
+// combination of the two maps of a differential attention.  Float32 arithmetic throughout.
+#include "common.cuh"
+
+#define MIX_MAX 4
+
+struct MixArgs {
+  const void* y[MIX_MAX];       // [T, W] each, activation type
+  const float* w[MIX_MAX];      // [W] each
+  int n;
+};
+
+// out[t, :] = coef * sum_i  y_i[t, :] / sqrt(mean(y_i[t, :]^2) + eps) * w_i
+template <typename TA>
+__global__ void rms_mix_kernel(MixArgs m, float coef, float eps, int W, TA* __restrict__ out) {
+  __shared__ float red[33];
+  __shared__ float f[MIX_MAX];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = 0; i < m.n; ++i) {
+    const TA* y = (const TA*)m.y[i] + (size_t)t * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = to_f32(y[c]); ss += v * v; }
+    const float tot = block_sum(ss, red);
+    if (threadIdx.x == 0) f[i] = rsqrtf(tot / (float)W + eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < m.n; ++i) acc += to_f32(((const TA*)m.y[i])[(size_t)t * W + c]) * f[i] * m.w[i][c];
+    out[(size_t)t * W + c] = from_f32<TA>(coef * acc);
+  }
+}
+
+extern "C" int gg_rms_mix(const void* const* ys, const float* const* ws, int n, float coef, float eps, int T, int W,
+                          int dtype, void* out, cudaStream_t stream) {
+  GG_REQUIRE(n >= 1 && n <= MIX_MAX, "rms_mix: %d branches are outside 1..%d", n, MIX_MAX);
+  GG_REQUIRE(T >= 0 && W > 0, "rms_mix: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  MixArgs m = {};
+  m.n = n;
+  for (int i = 0; i < n; ++i) { m.y[i] = ys[i]; m.w[i] = ws[i]; }
+  const int threads = W >= 1024 ? 256 : 128;
+  if (dtype == GG_F32) gg_launch(rms_mix_kernel<float>, dim3(T), dim3(threads), 0, stream, m, coef, eps, W, (float*)out);
+  else if (dtype == GG_BF16) gg_launch(rms_mix_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, m, coef, eps, W, (__nv_bfloat16*)out);
+  else return gg_fail(GG_ERR_INVALID, "rms_mix: unknown dtype %d", dtype);
+  return gg_check_launch("rms_mix");
+}
+
+// resid[i] += mult * (a[i] + b[i] + bias[i % W])          b, bias optional
+template <typename TA>
+__global__ void scaled_add_kernel(float* __restrict__ resid, const TA* __restrict__ a, const TA* __restrict__ b,
+                                  const float* __restrict__ bias, float mult, long long n, int W) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = to_f32(a[i]);
+    if (b) v += to_f32(b[i]);
+    if (bias) v += bias[i % W];
+    resid[i] += mult * v;
+  }
+}
+
+extern "C" int gg_scaled_add(float* resid, const void* a, const void* b, const float* bias, float mult, int T, int W,
+                             int dtype, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0 && a, "scaled_add: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * W;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(scaled_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, resid, (const float*)a, (const float*)b, bias, mult, n, W);
+  else if (dtype == GG_BF16) gg_launch(scaled_add_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, resid, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, bias, mult, n, W);
+  else return gg_fail(GG_ERR_INVALID, "scaled_add: unknown dtype %d", dtype);
+  return gg_check_launch("scaled_add");
+}
+
+// y[t, c] += bias[c]
+template <typename TA>
+__global__ void bias_add_kernel(TA* __restrict__ y, const float* __restrict__ bias, long long n, int W) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = from_f32<TA>(to_f32(y[i]) + bias[i % W]);
+}
+
+extern "C" int gg_bias_add(void* y, const float* bias, int T, int W, int dtype, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0 && bias, "bias_add: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * W;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(bias_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)y, bias, n, W);
+  else if (dtype == GG_BF16) gg_launch(bias_add_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)y, bias, n, W);
+  else return gg_fail(GG_ERR_INVALID, "bias_add: unknown dtype %d", dtype);
+  return gg_check_launch("bias_add");
+}
+
+// out[t, :] = [a[t, :] (+ da[t, :]), b[t, :]] rounded to the activation type; a, b float32 [T, W]
+template <typename TA>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const TA* __restrict__ da, const float* __restrict__ b,
+                                   TA* __restrict__ out, long long n, int W) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / W;
+    const int c = (int)(i - t * W);
+    out[t * 2 * W + c] = from_f32<TA>(a[i] + (da ? to_f32(da[i]) : 0.f));
+    out[t * 2 * W + W + c] = from_f32<TA>(b[i]);
+  }
+}
+
+extern "C" int gg_concat_cast(const float* a, const void* da, const float* b, void* out, int T, int W, int dtype,
+                              cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && W > 0, "concat_cast: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * W;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (dtype == GG_F32) gg_launch(concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, (const float*)da, b, (float*)out, n, W);
+  else if (dtype == GG_BF16) gg_launch(concat_cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, a, (const __nv_bfloat16*)da, b, (__nv_bfloat16*)out, n, W);
+  else return gg_fail(GG_ERR_INVALID, "concat_cast: unknown dtype %d", dtype);
+  return gg_check_launch("concat_cast");
+}
+
+// Clamped gated activation on [T, 2I] -> [T, I]:
+//   g = min(gate, limit); u = clamp(up, -limit, limit); out = g * sigmoid(alpha * g) * (u + shift)
+template <typename TA>
+__global__ void clamped_gate_kernel(const TA* __restrict__ gu, TA* __restrict__ out, long long n, int I, float limit,
+                                    float alpha, float shift) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / I;
+    const int c = (int)(i - t * I);
+    const float g = fminf(to_f32(gu[t * 2 * I + c]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * I + I + c]), -limit), limit);
+    out[i] = from_f32<TA>(g / (1.f + expf(-alpha * g)) * (u + shift));
+  }
+}
+
+extern "C" int gg_clamped_gate(const void* gu, void* out, int T, int I, float limit, float alpha, float shift, int dtype,
+                               cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && I > 0, "clamped_gate: bad sizes T=%d I=%d", T, I);
+  if (T == 0) return GG_OK;
+  const long long n = (long long)T * I;
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  if (dtype == GG_F32) gg_launch(clamped_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, n, I, limit, alpha, shift);
+  else if (dtype == GG_BF16) gg_launch(clamped_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, I, limit, alpha, shift);
+  else return gg_fail(GG_ERR_INVALID, "clamped_gate: unknown dtype %d", dtype);
+  return gg_check_launch("clamped_gate");
+}
+
+// Differential attention: the two maps of a head, a [T, 2H, dv] float32 with the maps of kv
+// group g laid out as [g][map][head in group], are combined as
+//   o = a1 - lambda * a2;  out[t, h, :] = o / sqrt(mean(o^2) + eps) * post
+// grid (T, H).
+template <typename TA>
+__global__ void diff_combine_kernel(const float* __restrict__ a, TA* __restrict__ out, float lambda, float eps,
+                                    float post, int H, int G, int dv) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y, rep = H / G, g = h / rep, j = h - g * rep;
+  const float* a1 = a + ((size_t)t * 2 * H + (size_t)(g * 2) * rep + j) * dv;
+  const float* a2 = a + ((size_t)t * 2 * H + (size_t)(g * 2 + 1) * rep + j) * dv;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) { const float o = a1[c] - lambda * a2[c]; ss += o * o; }
+  const float f = rsqrtf(block_sum(ss, red) / (float)dv + eps) * post;
+  TA* y = out + ((size_t)t * H + h) * dv;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) y[c] = from_f32<TA>((a1[c] - lambda * a2[c]) * f);
+}
+
+extern "C" int gg_diff_combine(const float* a, void* out, float lambda, float eps, float post, int T, int H, int G,
+                               int dv, int dtype, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dv > 0 && H <= 65535, "diff_combine: bad sizes T=%d H=%d G=%d dv=%d", T, H, G, dv);
+  if (T == 0) return GG_OK;
+  const int threads = dv >= 256 ? 256 : (dv >= 128 ? 128 : 64);
+  const dim3 grid(T, H);
+  if (dtype == GG_F32) gg_launch(diff_combine_kernel<float>, grid, dim3(threads), 0, stream, a, (float*)out, lambda, eps, post, H, G, dv);
+  else if (dtype == GG_BF16) gg_launch(diff_combine_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, a, (__nv_bfloat16*)out, lambda, eps, post, H, G, dv);
+  else return gg_fail(GG_ERR_INVALID, "diff_combine: unknown dtype %d", dtype);
+  return gg_check_launch("diff_combine");
+}

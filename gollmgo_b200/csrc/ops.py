@@ -660,3 +660,168 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, wgt: torch.Tensor, shared:
     _cuda(y, place, wgt, shared, out)
     T, D = out.shape
     _check(lib().gg_moe_combine(_p(y), _p(place), _p(wgt), _p(shared), _p(out), T, D, top, dtype_code(out.dtype), _stream()))
+
+
+# ---------------------------------------------------------------- attention of any make (general kernels)
+def rope_kv_write_x(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                    inv_freq: Optional[torch.Tensor], magnitude: float, bias: Optional[torch.Tensor],
+                    kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], nh: int, nkv: int, d: int,
+                    nv: int, dv: int, page_size: int, interleaved: bool = False, write_cache: bool = True) -> None:
+    """Rows [nh*d | nkv*d | nv*dv] of qkv: ``bias`` (float32, the row's width) is added, the first
+    2 * len(inv_freq) values of every q and k head are rotated (cosines and sines times
+    ``magnitude``), k goes to kcache [pages, nkv, page, d] and v to vcache [pages, nv, page, dv]
+    at slot_mapping[t]."""
+    _cuda(positions, slot_mapping, inv_freq, bias, kcache, vcache)
+    width = (nh + nkv) * d + nv * dv
+    if qkv.stride(1) != 1 or qkv.shape[1] < width:
+        raise KernelError("rope_kv_write_x: rows are not contiguous or too short")
+    if inv_freq is not None and inv_freq.dtype != torch.float64:
+        raise KernelError("rope_kv_write_x: inverse frequencies must be float64")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != width):
+        raise KernelError("rope_kv_write_x: the bias is float32 of the row's width")
+    if kcache is not None and (kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype):
+        raise KernelError("rope_kv_write_x: cache and activations differ in dtype")
+    rot = 2 * inv_freq.numel() if inv_freq is not None else 0
+    _check(lib().gg_rope_kv_write_x(_p(qkv), ctypes.c_longlong(qkv.stride(0)), dtype_code(qkv.dtype), _p(positions),
+                                    _p(slot_mapping), _p(inv_freq), ctypes.c_float(magnitude), _p(bias), _p(kcache),
+                                    _p(vcache), qkv.shape[0], nh, nkv, d, nv, dv, rot, page_size, int(interleaved),
+                                    int(write_cache), _stream()))
+
+
+def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                   block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
+                   tile_seq: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, out: torch.Tensor, nh: int, nkv: int,
+                   d: int, dv: int, v_share: int, page_size: int, window: int, scale: float, softcap: float) -> None:
+    """Causal attention of prompt portions (tiles of 16 queries) with keys of size d, values of
+    size dv, ``v_share`` key heads to a value head, optional window and capped scores; out
+    [T, nh*dv] in the cache's type or float32."""
+    _check(lib().gg_attn_prefill_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
+                                   _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(tile_seq),
+                                   _p(tile_q0), num_tiles, _p(out), int(out.dtype == torch.float32 and kcache.dtype != torch.float32),
+                                   nh, nkv, d, dv, v_share, page_size, window, ctypes.c_float(scale),
+                                   ctypes.c_float(softcap), _stream()))
+
+
+def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                  block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
+                  dec_seqs: torch.Tensor, n_dec: int, num_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor,
+                  out: torch.Tensor, nh: int, nkv: int, d: int, dv: int, v_share: int, page_size: int, window: int,
+                  scale: float, softcap: float) -> None:
+    """The same for single decoded tokens, split over the context and merged."""
+    if part_o.numel() < n_dec * nh * num_splits * dv or part_ml.numel() < n_dec * nh * num_splits * 2:
+        raise KernelError("attn_decode_x: scratch too small")
+    _check(lib().gg_attn_decode_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
+                                  _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(dec_seqs), n_dec,
+                                  num_splits, _p(part_o), _p(part_ml), _p(out),
+                                  int(out.dtype == torch.float32 and kcache.dtype != torch.float32), nh, nkv, d, dv,
+                                  v_share, page_size, window, ctypes.c_float(scale), ctypes.c_float(softcap),
+                                  _stream()), 2)
+
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, lam: float, eps: float, post: float, heads: int,
+                 kv_heads: int, dv: int) -> None:
+    """maps float32 [T, 2*heads*dv] laid out [kv group][map][head in group][dv]; out[t, h] =
+    rms-normed (map 1 - lam * map 2) * post, [T, heads*dv]."""
+    _cuda(maps, out)
+    T = out.shape[0]
+    if maps.dtype != torch.float32 or maps.numel() != 2 * out.numel() or out.shape[1] != heads * dv:
+        raise KernelError("diff_combine: maps float32 [T, 2 H dv], out [T, H dv]")
+    _check(lib().gg_diff_combine(_p(maps), _p(out), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(post),
+                                 T, heads, kv_heads, dv, dtype_code(out.dtype), _stream()))
+
+
+# ---------------------------------------------------------------- joining branches
+def rms_mix(ys, weights, coef: float, eps: float, out: torch.Tensor) -> None:
+    """out = coef * sum_i rmsnorm(ys[i]) * weights[i]; ys of out's shape and dtype, weights float32."""
+    _cuda(out, *ys, *weights)
+    T, W = out.shape
+    n = len(ys)
+    if n != len(weights) or any(y.shape != out.shape or y.dtype != out.dtype for y in ys) \
+            or any(w.dtype != torch.float32 or w.numel() != W for w in weights):
+        raise KernelError("rms_mix: branches of the output's shape and dtype, float32 weights of its width")
+    yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+    wp = (ctypes.c_void_p * n)(*[w.data_ptr() for w in weights])
+    _check(lib().gg_rms_mix(yp, wp, n, ctypes.c_float(coef), ctypes.c_float(eps), T, W, dtype_code(out.dtype),
+                            _p(out), _stream()))
+
+
+def scaled_add(resid: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], mult: float,
+               bias: Optional[torch.Tensor] = None) -> None:
+    """resid += mult * (a + b + bias): resid float32 [T, W], a and b of one dtype, bias float32 [W]."""
+    _cuda(resid, a, b, bias)
+    T, W = resid.shape
+    if resid.dtype != torch.float32 or a.shape != resid.shape or (b is not None and (b.shape != a.shape or b.dtype != a.dtype)):
+        raise KernelError("scaled_add: float32 residual, sublayer outputs of its shape and one dtype")
+    _check(lib().gg_scaled_add(_p(resid), _p(a), _p(b), _p(bias), ctypes.c_float(mult), T, W, dtype_code(a.dtype), _stream()))
+
+
+def bias_add(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[t, :] += bias (float32 [W]), in place."""
+    _cuda(y, bias)
+    if bias.dtype != torch.float32 or bias.numel() != y.shape[1]:
+        raise KernelError("bias_add: float32 bias of the rows' width")
+    _check(lib().gg_bias_add(_p(y), _p(bias), y.shape[0], y.shape[1], dtype_code(y.dtype), _stream()))
+
+
+def concat_cast(a: torch.Tensor, delta: Optional[torch.Tensor], b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] (+ delta[t]), b[t]] rounded to out's dtype; a, b float32 [T, W], out [T, 2W]."""
+    _cuda(a, delta, b, out)
+    T, W = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape or out.shape != (T, 2 * W) \
+            or (delta is not None and (delta.dtype != out.dtype or delta.shape != a.shape)):
+        raise KernelError("concat_cast: two float32 [T, W] in, [T, 2W] out")
+    _check(lib().gg_concat_cast(_p(a), _p(delta), _p(b), _p(out), T, W, dtype_code(out.dtype), _stream()))
+
+
+def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+    """g = min(gate, limit), u = clamp(up, -limit, limit): out = g * sigmoid(alpha * g) * (u + shift);
+    gate_up [T, 2I] (gates, then ups), out [T, I]."""
+    _cuda(gate_up, out)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError("clamped_gate: input must be [T, 2I] of the output's dtype")
+    _check(lib().gg_clamped_gate(_p(gate_up), _p(out), T, I, ctypes.c_float(limit), ctypes.c_float(alpha),
+                                 ctypes.c_float(shift), dtype_code(out.dtype), _stream()))
+
+
+# ---------------------------------------------------------------- gated delta rule
+def delta_prep(x: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, cu_q_lens: torch.Tensor, context_lens: torch.Tensor, state_slots: torch.Tensor,
+               num_seqs: int, kv_heads: int, heads: int, d: int, dv: int, qkv_out: torch.Tensor, beta: torch.Tensor,
+               decay: torch.Tensor) -> None:
+    """Short convolution + SiLU of the q, k, v channels of x [T, >= C] (C = 2*kv_heads*d + heads*dv)
+    with the window carried in conv_state [slots, taps-1, C]; q and k made unit vectors (q times
+    d^-1/2); beta = sigmoid(ba[:, :H]), decay = exp(-exp(a_log) * softplus(ba[:, H:] + dt_bias)).
+    Then the window is moved on.  Outputs float32."""
+    _cuda(conv_w, conv_state, ba, a_log, dt_bias, qkv_out, beta, decay)
+    C, taps = conv_w.shape
+    if x.stride(1) != 1 or C != 2 * kv_heads * d + heads * dv or conv_w.dtype != torch.float32 \
+            or conv_state.dtype != torch.float32 or ba.dtype != torch.float32 or qkv_out.dtype != torch.float32:
+        raise KernelError("delta_prep: bad shapes or dtypes")
+    _check(lib().gg_delta_prep(_p(x), ctypes.c_longlong(x.stride(0)), dtype_code(x.dtype), _p(conv_w), _p(conv_state),
+                               _p(ba), _p(a_log), _p(dt_bias), _p(cu_q_lens), _p(context_lens), _p(state_slots),
+                               x.shape[0], num_seqs, kv_heads, heads, d, dv, taps, _p(qkv_out), _p(beta), _p(decay),
+                               _stream()), 2 if taps > 1 else 1)
+
+
+def delta_recur(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                cu_q_lens: torch.Tensor, context_lens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
+                kv_heads: int, heads: int, d: int, dv: int, o_raw: torch.Tensor) -> None:
+    """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over every sequence's
+    tokens of the step, from and to state [slots, heads, dv, d] float32."""
+    _cuda(qkv, beta, decay, state, o_raw)
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dv, d):
+        raise KernelError("delta_recur: state must be float32 [slots, heads, dv, d]")
+    _check(lib().gg_delta_recur(_p(qkv), _p(beta), _p(decay), _p(state), _p(cu_q_lens), _p(context_lens),
+                                _p(state_slots), num_seqs, kv_heads, heads, d, dv, _p(o_raw), _stream()))
+
+
+def delta_out(o_raw: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int, dv: int,
+              out: torch.Tensor) -> None:
+    """out[t, h] = o / sqrt(mean(o^2) + eps) * weight * silu(gate[t, h]); gate is a column view
+    [T, heads*dv] of the projection's output."""
+    _cuda(o_raw, weight, out)
+    if gate.stride(1) != 1 or gate.dtype != out.dtype or weight.dtype != torch.float32:
+        raise KernelError("delta_out: gate rows contiguous and of the output's dtype, float32 weight")
+    _check(lib().gg_delta_out(_p(o_raw), _p(gate), ctypes.c_longlong(gate.stride(0)), dtype_code(out.dtype), _p(weight),
+                              ctypes.c_float(eps), out.shape[0], heads, dv, _p(out), _stream()))

@@ -178,3 +178,102 @@ extern "C" int gg_rope_kv_write(void* qkv, int act_dtype, const int* positions,
     return gg_fail(GG_ERR_INVALID, "rope_kv_write: unknown dtype %d", act_dtype);
   return gg_check_launch("rope_kv_write");
 }
+
+// The same for projections of any make: key heads of size d and value heads of size dv in
+// numbers of their own, an optional bias on the whole row (added first, in float32), rotation
+// of the first `rot` values of every q and k head, and a factor `mag` on every cosine and sine
+// (rotary tables that are stretched for long contexts scale both).
+// row:   [nh*d | nkv*d | nv*dv]
+// cache: K [num_pages, nkv, page_size, d], V [num_pages, nv, page_size, dv]
+template <typename TA>
+__global__ void rope_kv_write_x_kernel(TA* __restrict__ qkv, long long row_stride, const int* __restrict__ positions,
+                                       const int* __restrict__ slot_mapping, const double* __restrict__ inv_freq,
+                                       float mag, const float* __restrict__ bias, TA* __restrict__ kcache,
+                                       TA* __restrict__ vcache, int nh, int nkv, int d, int nv, int dv, int rot,
+                                       int page_size, int interleaved, int write_cache) {
+  extern __shared__ float cs[];        // cos[rot/2], sin[rot/2]
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  const int h0 = blockIdx.y * ROPE_HEADS_PER_CTA;
+  const int h1 = min(h0 + ROPE_HEADS_PER_CTA, nh + nkv + nv);
+  if (inv_freq && h0 < nh + nkv) {
+    const double pos = (double)positions[t];
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+      const double ang = pos * inv_freq[p];
+      const float r = (float)(ang - two_pi * rint(ang * (1.0 / two_pi)));
+      float s, c;
+      sincosf(r, &s, &c);
+      cs[p] = c * mag;
+      cs[half + p] = s * mag;
+    }
+  }
+  const int slot = (write_cache && slot_mapping) ? slot_mapping[t] : -1;
+  __syncthreads();
+  pdl_wait();
+  const int page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? slot - page * page_size : 0;
+  TA* row = qkv + (size_t)t * row_stride;
+  for (int h = h0; h < h1; ++h) {
+    if (h < nh + nkv) {
+      TA* x = row + (size_t)h * d;
+      const float* b = bias ? bias + (size_t)h * d : nullptr;
+      TA* kc = (h >= nh && slot >= 0) ? kcache + (((size_t)page * nkv + (h - nh)) * page_size + off) * d : nullptr;
+      const int nrot = inv_freq ? half : 0;
+      for (int p = threadIdx.x; p < nrot; p += blockDim.x) {
+        const int i0 = interleaved ? 2 * p : p;
+        const int i1 = interleaved ? 2 * p + 1 : p + half;
+        const float u = to_f32(x[i0]) + (b ? b[i0] : 0.f), v = to_f32(x[i1]) + (b ? b[i1] : 0.f);
+        const float c = cs[p], s = cs[half + p];
+        const TA ru = from_f32<TA>(u * c - v * s);
+        const TA rv = from_f32<TA>(v * c + u * s);
+        x[i0] = ru;
+        x[i1] = rv;
+        if (kc) { kc[i0] = ru; kc[i1] = rv; }
+      }
+      for (int c = 2 * nrot + threadIdx.x; c < d; c += blockDim.x) {
+        const TA y = b ? from_f32<TA>(to_f32(x[c]) + b[c]) : x[c];
+        if (b) x[c] = y;
+        if (kc) kc[c] = y;
+      }
+    } else {
+      const int hv = h - nh - nkv;
+      TA* x = row + (size_t)(nh + nkv) * d + (size_t)hv * dv;
+      const float* b = bias ? bias + (size_t)(nh + nkv) * d + (size_t)hv * dv : nullptr;
+      TA* vcp = slot >= 0 ? vcache + (((size_t)page * nv + hv) * page_size + off) * dv : nullptr;
+      if (!b && !vcp) continue;
+      for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        const TA y = b ? from_f32<TA>(to_f32(x[c]) + b[c]) : x[c];
+        if (b) x[c] = y;
+        if (vcp) vcp[c] = y;
+      }
+    }
+  }
+}
+
+extern "C" int gg_rope_kv_write_x(void* qkv, long long row_stride, int act_dtype, const int* positions,
+                                  const int* slot_mapping, const double* inv_freq, float mag, const float* bias,
+                                  void* kcache, void* vcache, int T, int nh, int nkv, int d, int nv, int dv, int rot,
+                                  int page_size, int interleaved, int write_cache, cudaStream_t stream) {
+  GG_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && d > 0 && nv > 0 && dv > 0 && page_size > 0,
+             "rope_kv_write_x: bad sizes T=%d nh=%d nkv=%d d=%d nv=%d dv=%d page=%d", T, nh, nkv, d, nv, dv, page_size);
+  GG_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_kv_write_x: rotary width %d must be even and <= head size %d", rot, d);
+  GG_REQUIRE(row_stride >= (long long)(nh + nkv) * d + (long long)nv * dv, "rope_kv_write_x: rows of %lld values are too short", row_stride);
+  GG_REQUIRE(!write_cache || (kcache && vcache && slot_mapping), "rope_kv_write_x: cache write without cache or slots");
+  if (T == 0) return GG_OK;
+  if (rot == 0) inv_freq = nullptr;
+  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+  GG_REQUIRE(smem <= 48 * 1024, "rope_kv_write_x: rotary width %d too large", rot);
+  const int big = d > dv ? d : dv;
+  const int threads = big >= 256 ? 128 : 64;
+  const dim3 grid(T, (nh + nkv + nv + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
+  GG_REQUIRE(grid.y <= 65535, "rope_kv_write_x: too many heads");
+  if (act_dtype == GG_F32)
+    gg_launch(rope_kv_write_x_kernel<float>, grid, dim3(threads), smem, stream, (float*)qkv, row_stride, positions, slot_mapping, inv_freq, mag, bias, (float*)kcache, (float*)vcache, nh, nkv, d, nv, dv, rot, page_size, interleaved, write_cache);
+  else if (act_dtype == GG_BF16)
+    gg_launch(rope_kv_write_x_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, inv_freq, mag, bias, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, nkv, d, nv, dv, rot, page_size, interleaved, write_cache);
+  else
+    return gg_fail(GG_ERR_INVALID, "rope_kv_write_x: unknown dtype %d", act_dtype);
+  return gg_check_launch("rope_kv_write_x");
+}

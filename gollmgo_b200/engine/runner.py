@@ -65,7 +65,7 @@ class ModelRunner:
         needs = self.model.cache_needs()
         self.num_pages = engine_config.num_blocks or self._pages_from_memory(needs)
         self.cache = CacheManager(needs, engine_config.block_size, self.num_pages,
-                                  max_requests=max(engine_config.max_batch_size, 4) * 2,
+                                  max_requests=engine_config.state_slots or max(engine_config.max_batch_size, 4) * 2,
                                   dtype=self.dtype, device=self.device)
         self.caches = [self._cache_view(i, n) for i, n in enumerate(needs)]
         self.builder = BatchBuilder(self.cache, self.device, query_tiles=self.model.query_tiles())
@@ -99,11 +99,7 @@ class ModelRunner:
         return max(64, avail // per_page)
 
     def _cache_view(self, cache_id: int, need):
-        if isinstance(need, PagedKVNeed):
-            return self.cache.layer_cache(cache_id)
-        if need is None:
-            return None
-        return self.cache.state_buffers[cache_id]
+        return self.cache.cache_view(cache_id, need)
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id) -> None:
@@ -227,12 +223,19 @@ class ModelRunner:
         batch.prev_tokens = self.last_tokens
         if cs.graph is None:
             torch.cuda.synchronize(self.device)
-            # warm-up on a side stream, then capture
+            # warm-up on a side stream, then capture.  The warm-up really runs the step; writing the
+            # same keys and values twice changes nothing, but recurrent state would move on twice,
+            # so the state of the step's requests is put back before the captured step is replayed
+            slots = torch.tensor(batch.state_slot_list, dtype=torch.long, device=self.device)
+            saved = [(buf, buf[slots].clone()) for buf in self.cache.state_buffers.values()]
             s = torch.cuda.Stream(self.device)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 self.model.forward(batch, self.caches)
             torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            for buf, rows in saved:
+                buf[slots] = rows
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             before = ops.launches

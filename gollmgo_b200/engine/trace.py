@@ -34,7 +34,7 @@ def make_trace_runner(model_dir: str, dtype: str, max_tokens: int, block_size: i
     ecfg = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=max_tokens // block_size,
                         max_batch_size=max(2 * max_live, 8),
                         max_token_budget=min(token_budget, max_tokens),
-                        max_model_len=max_tokens, cuda_graphs=cuda_graphs)
+                        max_model_len=max_tokens, cuda_graphs=cuda_graphs, state_slots=max_live)
     return ModelRunner(read_config_json(model_dir), ecfg, weights=model_dir)
 
 

@@ -112,7 +112,17 @@ def decode_splits(n_dec: int, ctas_per_split: int, num_sms: int, cluster_capacit
 
 class Attention:
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (None = all
-    keys), position (PartSpec)."""
+    keys), position (PartSpec); optional: v_head_dim (values of another size than keys),
+    scale (of the scores; default head_dim^-1/2), softcap (scores pass cap * tanh(score / cap)),
+    names (local names of the q, k, v, o tensors), out_buffer (name of the workspace buffer the
+    result is left in, for a mixer that runs beside another).
+
+    Values of another size, shared value heads (``v_share``, set by a subclass) or capped
+    scores run on the general kernels (csrc/attention.cu: float32 arithmetic whatever the cache's
+    type); the tensor-core kernels take the plain case."""
+
+    v_share = 1                  # consecutive key heads that read one value head
+    bias = False                 # q, k, v and o have biases (local name + ".b")
 
     def __init__(self, spec, ctx):
         self.ctx = ctx
@@ -120,33 +130,42 @@ class Attention:
         self.nh = int(spec["num_heads"])
         self.nkv = int(spec["num_kv_heads"])
         self.d = int(spec["head_dim"])
+        self.dv = int(spec.get("v_head_dim") or self.d)
         self.window = spec.get("window") or None
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} heads are not a multiple of {self.nkv} kv heads")
-        if self.d > 256:
-            raise ValueError(f"head size {self.d} is beyond what the attention kernels take (256)")
+        if self.d > 256 or self.dv > 256:
+            raise ValueError(f"head size {max(self.d, self.dv)} is beyond what the attention kernels take (256)")
         self.position = build_position(spec["position"], ctx)
-        self.scale = 1.0 / math.sqrt(self.d)
-        self.qkv_width = (self.nh + 2 * self.nkv) * self.d
+        self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.d))
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.names = tuple(spec.get("names") or ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"))
+        self.out_buffer = spec.get("out_buffer") or "mixer_out"
+        self.nv = self.nkv // self.v_share
+        self.general = (self.dv != self.d or self.softcap > 0 or self.v_share > 1 or self.bias
+                        or float(getattr(self.position, "magnitude", 1.0)) != 1.0)
+        self.qkv_width = (self.nh + self.nkv) * self.d + self.nv * self.dv
+        self.qkv_bias = None
+        self.o_bias = None
         self.num_sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count \
             if ctx.device.type == "cuda" else 148
         ws, T = ctx.workspace, ctx.max_tokens
         ws.reserve("qkv", T * self.qkv_width, ctx.act_dtype)
-        ws.reserve("attn_out", T * self.nh * self.d, ctx.act_dtype)
-        ws.reserve("mixer_out", T * self.hidden, ctx.act_dtype)
+        ws.reserve("attn_out", T * self.nh * self.dv, ctx.act_dtype)
+        ws.reserve(self.out_buffer, T * self.hidden, ctx.act_dtype)
         gchunks = -(-(self.nh // self.nkv) // 16)
         self._ctas_per_split = self.nkv * gchunks
         self._cluster_cap = None
-        if ctx.device.type == "cuda":
+        if ctx.device.type == "cuda" and not self.general:
             self._cluster_cap = [0] + [ops.attn_decode_cluster_capacity(ctx.act_dtype, self.d, s, self.nh // self.nkv)
                                        for s in range(1, ops.ATTN_MAX_CLUSTER + 1)]
         esize = torch.empty((), dtype=ctx.act_dtype).element_size()
         self._tile_bytes = TILE_KEYS * self.d * 2 * esize          # keys and values of one kv head
         rows = max(n * self._splits(n, TILE_KEYS << b) for n in range(1, ctx.max_seqs + 1)
                    for b in range(MAX_TILES.bit_length()))
-        ws.reserve("attn_part_o", rows * self.nh * self.d, torch.float32)
+        ws.reserve("attn_part_o", rows * self.nh * self.dv, torch.float32)
         ws.reserve("attn_part_ml", rows * self.nh * 2, torch.float32)
-        self._flat_ok = (ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
+        self._flat_ok = (not self.general and ctx.device.type == "cuda" and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128)
                          and ATTN_POLICY != "general" and FLAT_DECODE_FILL > 0
                          and ctx.max_seqs <= ops.ATTN_FLAT_MAX_SEQS)
         if self._flat_ok:
@@ -158,11 +177,15 @@ class Attention:
         self.w_o = None
 
     def cache_need(self):
+        if self.nv != self.nkv or self.dv != self.d:
+            return PagedKVNeed(self.nkv, self.d, self.window, v_heads=self.nv, v_head_dim=self.dv)
         return PagedKVNeed(self.nkv, self.d, self.window)
 
     def query_tiles(self):
         """The tile lists of the prompt kernels this mixer can end up using."""
         need = [TILES_GENERAL]
+        if self.general:
+            return need
         if self.ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and ATTN_POLICY != "general":
             need.append(TILES_MMA)
             if ATTN_POLICY == "auto":
@@ -196,20 +219,21 @@ class Attention:
         return (f"kv_slices={self._splits(n, facts.max_context)}",)
 
     def weights(self):
-        return {"q_proj.weight": WeightSpec((self.nh * self.d, self.hidden)),
-                "k_proj.weight": WeightSpec((self.nkv * self.d, self.hidden)),
-                "v_proj.weight": WeightSpec((self.nkv * self.d, self.hidden)),
-                "o_proj.weight": WeightSpec((self.hidden, self.nh * self.d))}
+        q, k, v, o = self.names
+        return {q: WeightSpec((self.nh * self.d, self.hidden)),
+                k: WeightSpec((self.nkv * self.d, self.hidden)),
+                v: WeightSpec((self.nv * self.dv, self.hidden)),
+                o: WeightSpec((self.hidden, self.nh * self.dv))}
 
     def load(self, get):
-        q, k, v = get("q_proj.weight"), get("k_proj.weight"), get("v_proj.weight")
+        q, k, v = (get(n) for n in self.names[:3])
         dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
         self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
-        self.w_o = get("o_proj.weight").contiguous()
+        self.w_o = get(self.names[3]).contiguous()
 
     # the optional protocol of parts/linear.py
     def takes_normed_rows(self, num_tokens):
-        return fuses_norms(num_tokens, self.w_qkv, self.ctx.act_dtype)
+        return not self.general and fuses_norms(num_tokens, self.w_qkv, self.ctx.act_dtype)
 
     def fuses_next_norm(self, num_tokens):
         return fuses_norms(num_tokens, self.w_o, self.ctx.act_dtype)
@@ -243,9 +267,46 @@ class Attention:
                             batch.context_lens, batch.dec_seqs, n, splits,
                             part_o, part_ml, out, self.nh, self.nkv, self.d, self.ctx.page_size, window, self.scale)
 
+    def attend_general(self, x, batch, cache, writes_cache, out):
+        """q, k, v projections, bias, rotation, cache write and attention on the general kernels;
+        fills ``out`` [T, nh * dv] (the activation type, or float32)."""
+        T = x.shape[0]
+        ws = self.ctx.workspace
+        kc, vc, group = cache
+        qkv = ws.get("qkv", T, self.qkv_width)
+        linear(x, self.w_qkv, qkv)
+        if hasattr(self.position, "apply"):
+            raise TypeError("a position encoding that rewrites q and k itself cannot be used with the general attention path")
+        ops.rope_kv_write_x(qkv, batch.positions, batch.slot_mapping[group], self.position.rope_table(),
+                            float(getattr(self.position, "magnitude", 1.0)), self.qkv_bias, kc, vc, self.nh, self.nkv,
+                            self.d, self.nv, self.dv, self.ctx.page_size, self.position.interleaved, writes_cache)
+        window = int(self.window or 0)
+        bt = batch.block_tables[group]
+        if batch.num_portions:
+            if TILES_GENERAL not in batch.tiles:
+                raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
+                                   "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
+            t16 = batch.tiles[TILES_GENERAL]
+            ops.attn_prefill_x(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                               t16.seq, t16.q0, t16.count, out, self.nh, self.nkv, self.d, self.dv, self.v_share,
+                               self.ctx.page_size, window, self.scale, self.softcap)
+        if batch.num_decode:
+            n = batch.num_decode
+            facts = getattr(batch, "facts", None)
+            longest = facts.max_context if facts is not None else max(s + q for s, q in zip(batch.q_starts, batch.q_lens))
+            splits = self._splits(n, longest)
+            ops.attn_decode_x(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
+                              batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * self.nh * splits * self.dv),
+                              ws.get("attn_part_ml", 1, n * self.nh * splits * 2), out, self.nh, self.nkv, self.d,
+                              self.dv, self.v_share, self.ctx.page_size, window, self.scale, self.softcap)
+        return out
+
     def forward(self, x, batch, cache, writes_cache=True, then=None):
         T = x.shape[0]
         ws = self.ctx.workspace
+        if self.general:
+            out = self.attend_general(x, batch, cache, writes_cache, ws.get("attn_out", T, self.nh * self.dv))
+            return linear(out, self.w_o, ws.get(self.out_buffer, T, self.hidden), then)
         kc, vc, group = cache
         qkv = ws.get("qkv", T, self.qkv_width)
         linear(x, self.w_qkv, qkv)
@@ -282,7 +343,7 @@ class Attention:
                              num_tiles128=t128.count if t128 else 0, allow_tc=t128 is not None)
         if batch.num_decode:
             self._decode(qkv, kc, vc, group, batch, out, window, flat_step, fused, table, writes_cache)
-        y = ws.get("mixer_out", T, self.hidden)
+        y = ws.get(self.out_buffer, T, self.hidden)
         return linear(out, self.w_o, y, then)
 
 

@@ -144,5 +144,33 @@ class PostNormBlock:
         return ResidualRows(nxt)
 
 
+class ParallelBlock:
+    """x += mult * (mixer(h) + ff(h)) with h = norm(x): one norm, and both sublayers read its
+    output.  A layer without a feed-forward adds the mixer alone.  params: residual_mult (default 1).
+    The sum of the sublayers and the add to the stream are float32 (one kernel)."""
+
+    def __init__(self, layer_spec, mixer, feed_forward, mixer_norm, ffn_norm, ctx):
+        self.mixer, self.feed_forward, self.mixer_norm, self.ctx = mixer, feed_forward, mixer_norm, ctx
+        if ffn_norm is not None:
+            raise ValueError("a parallel block has one norm; the feed-forward reads the mixer's")
+        self.hidden = mixer_norm.size
+        self.mult = float(layer_spec.block.get("residual_mult", 1.0))
+        ctx.workspace.reserve("normed", ctx.max_tokens * self.hidden, ctx.act_dtype)
+
+    def forward(self, resid, delta, batch, cache, writes_cache=True):
+        T = resid.shape[0]
+        if isinstance(delta, ResidualRows):
+            delta = None                                  # the block before has added everything itself
+        elif delta is not None and not torch.is_tensor(delta):
+            raise ValueError("a parallel block cannot take the norm's input from the block before it")
+        h = self.ctx.workspace.get("normed", T, self.hidden)
+        self.mixer_norm.add_norm(resid, delta, h)
+        a = self.mixer.forward(h, batch, cache, writes_cache)
+        f = self.feed_forward.forward(h, batch) if self.feed_forward is not None else None
+        ops.scaled_add(resid, a, f, self.mult)
+        return None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("parallel", ParallelBlock)
 register_block("post_norm", PostNormBlock)

@@ -13,16 +13,23 @@ from .registry import register_feed_forward
 
 
 class GatedMLP:
-    """params: hidden_size, intermediate_size, activation ("silu"), names (optional: the local
-    names of the gate, up and down tensors; default the Llama checkpoint's)."""
+    """params: hidden_size, intermediate_size, activation, names (optional: the local names of the
+    gate, up and down tensors; default the Llama checkpoint's).  Activations: "silu" = silu(gate) * up;
+    "clamped_swish" = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit) and u = clamp(up,
+    -limit, limit) (params limit, alpha = 1.702, shift = 1)."""
 
     def __init__(self, spec, ctx):
         self.ctx = ctx
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
         act = spec.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"activation {act!r} is not supported (known: silu)")
+        if act not in ("silu", "clamped_swish"):
+            raise ValueError(f"activation {act!r} is not supported (known: silu, clamped_swish)")
+        self.activation = act
+        if act == "clamped_swish":
+            self.limit = float(spec["limit"])
+            self.alpha = float(spec.get("alpha", 1.702))
+            self.shift = float(spec.get("shift", 1.0))
         self.names = tuple(spec.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         ws, T = ctx.workspace, ctx.max_tokens
         ws.reserve("gate_up", T * 2 * self.inter, ctx.act_dtype)
@@ -46,7 +53,7 @@ class GatedMLP:
     # the optional protocol of parts/linear.py: the first product can take a norm's unnormalised
     # input, the last one can do the residual add and prepare the next norm
     def takes_normed_rows(self, num_tokens):
-        return fuses_norms(num_tokens, self.w_gate_up, self.ctx.act_dtype)
+        return self.activation == "silu" and fuses_norms(num_tokens, self.w_gate_up, self.ctx.act_dtype)
 
     def fuses_next_norm(self, num_tokens):
         return fuses_norms(num_tokens, self.w_down, self.ctx.act_dtype)
@@ -55,7 +62,10 @@ class GatedMLP:
         T = x.shape[0]
         ws = self.ctx.workspace
         a = ws.get("ffn_act", T, self.inter)
-        if isinstance(x, NormedRows):
+        if self.activation == "clamped_swish":
+            gu = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.inter))
+            ops.clamped_gate(gu, a, self.limit, self.alpha, self.shift)
+        elif isinstance(x, NormedRows):
             ops.gemm_small_m(x.scaled, self.w_gate_up, a, gated=True, in_partials=x.partials,
                              hidden=x.hidden, eps=x.eps)
         elif ops.small_m_ok(x, self.w_gate_up):

@@ -53,6 +53,8 @@ def spec_manifest(spec: ModelSpec, parts=None, embed_position=None, blocks=None,
         m[spec.final_norm_name] = WeightSpec((spec.hidden_size,))
     if embed_position is not None:
         m.update(_prefixed(spec.embed_position_prefix, embed_position.weights()))
+    if spec.input_mix_name:
+        m[spec.input_mix_name] = WeightSpec((spec.hidden_size, 2 * spec.hidden_size))
     m[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), optional=spec.tie_embeddings)
     return m
 
@@ -75,6 +77,13 @@ class DecoderModel:
         ws = ctx.workspace
         ws.reserve("residual", ctx.max_tokens * spec.hidden_size, torch.float32)
         ws.reserve("head_in", ctx.max_tokens * spec.hidden_size, ctx.act_dtype)
+        self.mixes_input = any(e.mix_input for e in spec.run_order)
+        if self.mixes_input:
+            if not spec.input_mix_name:
+                raise ValueError("a run entry mixes the embedding output in, but the model names no tensor for it")
+            ws.reserve("embed_out", ctx.max_tokens * spec.hidden_size, torch.float32)
+            ws.reserve("mix_in", ctx.max_tokens * 2 * spec.hidden_size, ctx.act_dtype)
+        self.w_input_mix = None
         self.embed = None
         self.head = None
         self.bad_id = torch.zeros(1, dtype=torch.int32, device=ctx.device) \
@@ -102,6 +111,8 @@ class DecoderModel:
         self.final_norm.load(lambda local: get(s.final_norm_name + local))
         if self.embed_position is not None:
             self.embed_position.load(lambda local, p=s.embed_position_prefix: get(p + local))
+        if self.mixes_input:
+            self.w_input_mix = get(s.input_mix_name).contiguous()
         head = None if s.tie_embeddings else get(s.head_name)
         self.head = self.embed if head is None else head.contiguous()
 
@@ -112,7 +123,7 @@ class DecoderModel:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-        add(self.embed), add(self.head)
+        add(self.embed), add(self.head), add(self.w_input_mix)
         def add_part(part, depth=0):
             for v in vars(part).values():
                 if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.is_cuda:
@@ -172,11 +183,24 @@ class DecoderModel:
             self.embed_position.add_to_embedding(resid, batch)
         delta = None
         order = self.spec.run_order
+        x0 = None
+        if self.mixes_input:
+            x0 = ws.get("embed_out", T, H)
+            x0.copy_(resid)
         for i, e in enumerate(order):
             block = self.blocks[e.layer]
+            if e.mix_input:
+                # x <- W [x; x0]: both halves rounded to the activation type for the product, the
+                # result float32 straight into the stream (what the block before still owes is added first)
+                if not (delta is None or isinstance(delta, ResidualRows) or torch.is_tensor(delta)):
+                    raise ValueError("the block before an input mix handed on a norm's input instead of its output")
+                cat = ws.get("mix_in", T, 2 * H)
+                ops.concat_cast(resid, delta if torch.is_tensor(delta) else None, x0, cat)
+                linear(cat, self.w_input_mix, resid)
+                delta = None
             if getattr(block, "chains_norms", False):
                 # such a block may fold the first norm of the block that runs next into its last product
-                nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+                nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) and not order[i + 1].mix_input else None
                 delta = block.forward(resid, delta, batch, caches[e.cache], e.writes_cache, next_block=nxt)
             else:
                 delta = block.forward(resid, delta, batch, caches[e.cache], e.writes_cache)

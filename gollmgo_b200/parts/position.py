@@ -9,6 +9,7 @@ and writes the cache.
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 
 import torch
 
@@ -20,6 +21,18 @@ def inverse_frequencies(rot: int, theta: float, scaling) -> torch.Tensor:
     f = torch.pow(torch.tensor(theta, dtype=torch.float64), -p / rot)
     if scaling is None:
         return f
+    if scaling.rope_type == "yarn":
+        # Frequencies whose wave turns fewer than `slow` times over the original length are divided by
+        # the factor, those that turn more than `fast` times are kept, and a linear ramp over the pair
+        # index joins the two: with turns(i) = original * f_i / (2 pi), the pair index at which a wave
+        # makes t turns is rot * ln(original / (2 pi t)) / (2 ln theta).
+        def index_of(turns):
+            return rot * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo = max(math.floor(index_of(scaling.fast)), 0)
+        hi = min(math.ceil(index_of(scaling.slow)), rot - 1)
+        i = torch.arange(0, rot // 2, dtype=torch.float64)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / scaling.factor * ramp + f * (1.0 - ramp)
     if scaling.rope_type == "linear":
         return f / scaling.factor
     if scaling.rope_type == "llama3":
@@ -33,9 +46,25 @@ def inverse_frequencies(rot: int, theta: float, scaling) -> torch.Tensor:
     raise ValueError(f"rope scaling {scaling.rope_type!r} is not supported")
 
 
+@dataclass(frozen=True)
+class YarnScaling:
+    """Stretching of a rotary table for contexts beyond the ``original`` length by ``factor``:
+    slow waves are slowed, fast ones kept, and every cosine and sine grows by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    rope_type: str = "yarn"
+
+    @property
+    def magnitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
+
+
 class RotaryEncoding:
-    """params: head_dim, theta, scaling (config.RopeScaling or None), interleaved,
-    rotary_dim (defaults to head_dim)."""
+    """params: head_dim, theta, scaling (config.RopeScaling, YarnScaling or None), interleaved,
+    rotary_dim (defaults to head_dim).  ``magnitude`` is a factor on every cosine and sine (1 unless
+    the scaling says otherwise); only the kernels of the general attention path apply it."""
 
     def __init__(self, spec, ctx):
         self.head_dim = int(spec["head_dim"])
@@ -43,6 +72,7 @@ class RotaryEncoding:
         if self.rot % 2 or self.rot > self.head_dim:
             raise ValueError(f"rotary width {self.rot} must be even and at most {self.head_dim}")
         self.interleaved = bool(spec.get("interleaved", False))
+        self.magnitude = float(getattr(spec.get("scaling"), "magnitude", 1.0))
         self._table = inverse_frequencies(self.rot, float(spec["theta"]), spec.get("scaling")) \
             .to(ctx.device).contiguous()
 

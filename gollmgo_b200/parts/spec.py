@@ -9,7 +9,8 @@ registry; no part knows which model it is in.
 The run order is a list of ``RunEntry``.  An entry names the layer to run and the
 cache entry it uses; a layer may be named twice (each occurrence with a cache
 entry of its own), and an entry with ``writes_cache=False`` reads the cache that
-another entry wrote instead of writing its own.
+another entry wrote instead of writing its own.  An entry with ``mix_input`` first
+remakes the stream from itself and the embedding output (``ModelSpec.input_mix_name``).
 """
 from __future__ import annotations
 
@@ -53,6 +54,9 @@ class RunEntry:
     layer: int
     cache: int                         # index of the cache entry this occurrence uses
     writes_cache: bool = True
+    # before this entry runs, the stream is remade from itself and the embedding output:
+    # x <- W [x; x0] with the tensor ModelSpec.input_mix_name ([width, 2 width], x first)
+    mix_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -78,6 +82,9 @@ class ModelSpec:
     # name patterns (fnmatch) of checkpoint tensors that this model does not use and a
     # checkpoint may still hold
     ignorable_tensors: Tuple[str, ...] = ()
+    # the tensor of the run entries' mix_input (a model that runs some of its layers several
+    # times feeds the embedding output back in at the start of every pass); "" = none
+    input_mix_name: str = ""
 
     @property
     def num_cache_entries(self) -> int:

@@ -46,6 +46,8 @@ class WeightSpec:
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" | "int"
     optional: bool = False       # may be absent (e.g. lm_head of a tied model)
+    init: str = ""               # how random weights are drawn where the shape does not say: "normal" (a
+                                 # vector that is no norm weight), "taps" (rows of a short convolution)
 
 
 # Tensors some exporters add that carry no parameters of the model.

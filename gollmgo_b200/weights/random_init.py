@@ -27,7 +27,12 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, device, dtype: torch.d
                   std: float = 0.02, norm_jitter: float = 0.0) -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
-    if len(spec.shape) == 1:                      # a norm's weight
+    if spec.init == "taps":                       # a short convolution: taps of the size of an average
+        t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+        t.normal_(0.0, 1.0 / spec.shape[-1], generator=gen)
+        t[..., -1] += 1.0
+        return t.to(dtype)
+    if len(spec.shape) == 1 and spec.init != "normal":      # a norm's weight
         t = torch.ones(spec.shape, dtype=torch.float32, device=device)
         if norm_jitter:
             t += norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
