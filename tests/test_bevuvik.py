@@ -56,7 +56,7 @@ class MixerRun:
         self.kit, self.mixer, self.dtype = kit, mixer, dtype
         self.need = mixer.cache_need()
         self.cm = kit.CacheManager([self.need], page, pages, slots, dtype=dtype, device="cuda")
-        self.bb = kit.BatchBuilder(self.cm, "cuda", query_tiles=mixer.query_tiles())
+        self.bb = kit.BatchBuilder(self.cm, "cuda", query_tiles=getattr(mixer, "query_tiles", lambda: ())())
 
     def step(self, parts):
         """parts: {sequence: rows [n, width]} -> {sequence: output rows}"""
@@ -72,12 +72,14 @@ class MixerRun:
             at += rows.shape[0]
         return out
 
-    def feed(self, x, cuts, seq="s"):
+    def feed(self, x, cuts, seq="s", keep=False):
         outs, at = [], 0
         for c in cuts:
             outs.append(self.step({seq: x[at:at + c]})[seq])
             at += c
         assert at == x.shape[0]
+        if not keep:
+            self.cm.free(seq)
         return torch.cat(outs)
 
 
@@ -303,15 +305,14 @@ def test_differential_attention_at_the_windows_edge(kit, dtype, shape):
     x = torch.zeros(n, D)
     x[:, :C] = torch.randn(n, C, generator=g)
     # key tag t at position k; queries at k + W - 1 (the last that sees it) and k + W (the first that does not)
-    keys = [0, 1, page - 1, page, W + 3, 2 * W + 1, 2 * W + 40, 3 * W + 20]
-    queries = {}
+    keys = [0, 1, page - 1, page, W + 3, 2 * W + 7, 2 * W + 40, 3 * W + 20]
+    queries = []                                  # (query, tag); a query may carry two tags
     for t, k in enumerate(keys):
         x[k, C + t] = 8.0
-        for qi in (k + 1, k + W - 1, k + W):
-            if qi < n:
-                queries[qi] = t
-    for qi, t in queries.items():
+        queries += [(qi, t) for qi in (k + 1, k + W - 1, k + W) if qi < n]
+    for qi, t in queries:
         x[qi, C + TAGS + t] += 1.0
+    assert sum(qi in (keys[4] + W - 1, keys[4] + W) for qi, _ in queries) == 2      # those two carry one tag each
     x = bf(x)
     pw = {"p." + k: v for k, v in w.items()}
     want = P.differential_attention(x, pw, "p.", m, eps)
@@ -325,12 +326,13 @@ def test_differential_attention_at_the_windows_edge(kit, dtype, shape):
     run = MixerRun(kit, mixer, dtype, page, pages=4 * (W // page + 8))
     first = 2 * W + 35
     cuts = cuts_of(first, [W - 1, 2, 17, 3, page, 2, 50]) + [1] * (n - first)       # the later queries are decoded alone
-    close(run.feed(x, cuts, "a"), want, dtype)
-    close(run.feed(x, [n], "b"), want, dtype)                                         # all queries inside one portion
-    close(run.feed(x, cuts_of(n, [2, 5, W, 3, W + 1]), "c"), want, dtype)
+    close(run.feed(x, cuts, "a", keep=True), want, dtype)
     # the windowed group gave pages back as the window passed
     held = [p for p in run.cm.block_table("a", 0) if p >= 0]
     assert len(held) <= W // page + 2 < len(run.cm.block_table("a", 0))
+    run.cm.free("a")
+    close(run.feed(x, [n], "b"), want, dtype)                                         # all queries inside one portion
+    close(run.feed(x, cuts_of(n, [2, 5, W, 3, W + 1]), "c"), want, dtype)
 
 
 # ------------------------------------------------------------------ gated delta rule
@@ -415,9 +417,8 @@ def test_gated_delta_rule_remembers_far_back_and_slots_start_clean(kit, dtype):
     assert float((want[399] - want2[399]).abs().max()) > 0.02 * float(want[399].abs().max())     # token 3 still matters at 399
     run = MixerRun(kit, mixer, dtype, 16, slots=1)
     close(run.feed(x, cuts_of(380, [64, 2, 100, 7]) + [1] * 20, "first"), want, dtype, f32=1e-4, bf16=3e-2)
-    run.cm.free("first")
     y = bf(torch.randn(30, D, generator=g))
-    close(run.feed(y, [1, 2, 27], "second"), P.gated_delta_rule(y, pw, "p.", m, eps), dtype, f32=1e-4, bf16=3e-2)
+    close(run.feed(y, [1, 2, 27], "second", keep=True), P.gated_delta_rule(y, pw, "p.", m, eps), dtype, f32=1e-4, bf16=3e-2)
     assert run.cm.state_slot("second") == 0
 
 
