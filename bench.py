@@ -152,17 +152,27 @@ def reference_arm(args) -> int:
     return 0
 
 
+# --design: the design's shapes, each beside the closest model this engine had before it at equal
+# size.  Tekenex: a Llama decoder of equal width, depth, heads, head size and vocabulary with one
+# kv head (its cache rows are as wide as the latent's).  Bevuvik: a Llama decoder of equal width,
+# heads, kv heads, feed-forward width and vocabulary with as many layers as the Bevuvik shape runs
+# (the layers of its repeated run counted once per pass).
+DESIGN_PAIRS = {
+    "tekenex": [("tekenex_w2048", "llama_mqa_w2048"), ("tekenex_w4096", "llama_mqa_w4096")],
+    "bevuvik": [("bevuvik_w2048", "llama_gqa_w2048"), ("bevuvik_w4096", "llama_gqa_w4096")],
+}
+
+
 def design_bench(args) -> int:
-    """--design tekenex: prefill and decode throughput of Tekenex at sizes that resemble a real
-    model's layers (random weights), each beside the closest model this engine had before, a Llama
-    decoder of equal width, depth, heads, head size and vocabulary with one kv head (its cache
-    rows are as wide as the latent's).  One JSON line; the default workload is untouched."""
+    """--design NAME: prefill and decode throughput of that design at sizes that resemble a real
+    model's layers (random weights), each beside the closest model this engine had before.  One
+    JSON line; the default workload is untouched."""
     import torch
     from gollmgo_b200 import Engine, EngineConfig
     from gollmgo_b200.csrc import ops
     from gollmgo_b200.engine.batch import StepEntry
     W, K = max(args.warmup, 3), max(min(args.steps, 64), 1)
-    pairs = [("tekenex_w2048", "llama_mqa_w2048"), ("tekenex_w4096", "llama_mqa_w4096")]
+    pairs = DESIGN_PAIRS[args.design]
     batches = (1, 8, 64)
     rows = {}
     for shape in [s for pair in pairs for s in pair]:
@@ -220,7 +230,7 @@ def design_bench(args) -> int:
         eng.stop()
         del eng, runner
         torch.cuda.empty_cache()
-    print(json.dumps({"metric": "Tekenex beside the closest model at equal size: prefill of 2048 tokens and decode at context 2048",
+    print(json.dumps({"metric": f"{args.design.capitalize()} beside the closest model at equal size: prefill of 2048 tokens and decode at context 2048",
                       "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
                       "n_gpus": 1, "steps": K, "warmup": W, "pairs": pairs, "shapes": rows, "peaks": peaks()}))
     return 0
@@ -235,7 +245,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--design", default=None, choices=["tekenex"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGN_PAIRS),
                     help="instead of the default workload: that design at a few sizes beside the closest model at equal size")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -484,6 +484,7 @@ extern "C" int gg_attn_decode_cluster_capacity(int dtype, int d, int splits, int
 extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* kcache, const void* vcache,
                                  int dtype, const int* block_tables, int bt_stride, const int* cu_q_lens,
                                  const int* context_lens, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                 const int* tile64_seq, const int* tile64_q0, int num_tiles64, int allow_mma,
                                  void* out, int out_f32, int nh, int nkv, int d, int dv, int v_share,
                                  int page_size, int window, float scale, float softcap, cudaStream_t stream) {
   AttnArgs a = {};
@@ -495,6 +496,11 @@ extern "C" int gg_attn_prefill_x(const void* q, long long q_stride, const void* 
   a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   int rc = check_common(a, "attn_prefill_x");
   if (rc) return rc;
+  // bfloat16 with sizes of 64 or 128: the mma.sync kernel over tiles of 64 queries
+  if (allow_mma && tile64_seq && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0) {
+    a.tile_seq = tile64_seq; a.tile_q0 = tile64_q0;
+    return attn_prefill_mma_x(a, num_tiles64, stream);
+  }
   return attn_prefill_general(a, dtype, num_tiles, stream);
 }
 
@@ -503,7 +509,7 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
                                 const int* context_lens, const int* dec_seqs, int n_dec, int num_splits,
                                 float* part_o, float* part_ml, void* out, int out_f32, int nh, int nkv, int d,
                                 int dv, int v_share, int page_size, int window, float scale, float softcap,
-                                cudaStream_t stream) {
+                                int allow_mma, cudaStream_t stream) {
   AttnArgs a = {};
   a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_q_lens = cu_q_lens;
@@ -516,7 +522,10 @@ extern "C" int gg_attn_decode_x(const void* q, long long q_stride, const void* k
   GG_REQUIRE(n_dec >= 0 && num_splits >= 1 && num_splits <= 65535, "attn_decode_x: bad n_dec %d or splits %d", n_dec, num_splits);
   GG_REQUIRE(part_o && part_ml, "attn_decode_x: no scratch given");
   if (n_dec == 0) return GG_OK;
-  rc = attn_decode_general(a, dtype, n_dec, stream);
+  if (allow_mma && attn_mma_x_supported(dtype, d, dv > 0 ? dv : d, page_size) && q_stride % 8 == 0)
+    rc = attn_decode_mma_x(a, n_dec, stream);
+  else
+    rc = attn_decode_general(a, dtype, n_dec, stream);
   if (rc) return rc;
   return attn_merge_launch(a, dtype, n_dec, stream);
 }

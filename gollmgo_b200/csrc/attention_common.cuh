@@ -46,6 +46,10 @@ int attn_prefill_mma(const AttnArgs& a, int num_tiles, cudaStream_t stream);   /
 #define ATTN_MAX_CLUSTER 8       // slices of one token and kv head that can be one (portable) cluster
 int attn_decode_mma(const AttnArgs& a, int n_dec, cudaStream_t stream, bool* merged);
 int attn_decode_cluster_capacity(int d, int splits, int group);
+// the same with values of another size than keys, shared value heads, capped scores, float32 out (a.dv, a.v_share, a.softcap, a.out_f32)
+bool attn_mma_x_supported(int dtype, int d, int dv, int page_size);
+int attn_prefill_mma_x(const AttnArgs& a, int num_tiles, cudaStream_t stream);   // tiles of 64 queries
+int attn_decode_mma_x(const AttnArgs& a, int n_dec, cudaStream_t stream);        // partial results; the caller merges
 // large batches: the tiles of all (token, kv head) pairs cut into equal ranges, one per CTA
 int attn_decode_flat_ctas(int d);
 int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t stream);

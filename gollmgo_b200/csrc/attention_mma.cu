@@ -1020,3 +1020,295 @@ int attn_decode_flat(const AttnArgs& a, int n_dec, int* prefix, cudaStream_t str
   if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "attn_merge_flat: launch: %s", cudaGetErrorString(e));
   return gg_check_launch("attn_merge_flat");
 }
+
+// ---------------------------------------------------------------- keys and values of different sizes
+// The same two kernels for attention whose values have a size of their own (DK for queries and
+// keys, DV for values and the result, each 64 or 128), whose key heads may share value heads
+// (a.v_share consecutive key heads read one value head), and whose scores may be capped by
+// softcap * tanh(score / softcap).  The result is bfloat16 or (a.out_f32) float32.  Decode: one
+// CTA per (token, key head [x 16 heads of its group], slice), partial results to part_o /
+// part_ml for the merge kernel of attention.cu; no cluster, no rotation inside.
+template <int D>
+__device__ __forceinline__ void load_tile_of(const __nv_bfloat16* cache, int heads, int head, const int* bt, int k0,
+                                             int lo, int hi, unsigned dst, int ps_log2) {
+  constexpr int CPR = D / 8;
+  constexpr int ROWS_PER_PASS = MMA_THREADS / CPR;
+  const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+  const int ps_mask = (1 << ps_log2) - 1;
+  const size_t page_elems = (size_t)heads << ps_log2;
+  const unsigned in_head = ((unsigned)head << ps_log2);
+#pragma unroll
+  for (int i = 0; i < MMA_BK / ROWS_PER_PASS; ++i) {
+    const int row = r0 + i * ROWS_PER_PASS;
+    const int tok = k0 + row;
+    int page = -1;
+    if (tok >= lo && tok < hi) page = __ldg(bt + (tok >> ps_log2));
+    const size_t src = page >= 0 ? ((size_t)page * page_elems + in_head + (unsigned)(tok & ps_mask)) * D + ch * 8 : 0;
+    cp_async16(dst + tile_off<D>(row, ch), cache + src, page >= 0 ? 16 : 0);
+  }
+}
+
+// score (raw dot product) -> base-2 exponent: scaled, capped where the cap is positive
+__device__ __forceinline__ float score_exp2(float dot, float scale, float cap) {
+  float x = dot * scale;
+  if (cap > 0.f) x = cap * tanhf(x / cap);
+  return x * LOG2E;
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int K_BYTES = MMA_BK * DK * 2, V_BYTES = MMA_BK * DV * 2, STAGE = K_BYTES + V_BYTES;
+  constexpr int STAGES = 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  const int ps_log2 = 31 - __clz(a.page_size);
+  const int b = a.tile_seq[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
+  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int vsh = a.v_share > 1 ? a.v_share : 1, nv = a.nkv / vsh, vh = kvh / vsh;
+  const int t0 = a.cu_q_lens[b], qlen = a.cu_q_lens[b + 1] - t0;
+  const int ctx = a.context_lens[b];
+  const int qstart = ctx - qlen;
+  const int nrows = min(64, qlen - q0);
+  const int first = qstart + q0;
+  const int hi = first + nrows;
+  const int lo = a.window > 0 ? max(0, first - a.window + 1) : 0;
+  const int kstart = (lo / MMA_BK) * MMA_BK;
+  const int ntiles = (hi - kstart + MMA_BK - 1) / MMA_BK;
+  const int* bt = a.block_tables + (size_t)b * a.bt_stride;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
+  const unsigned base = smem_u32(smem_raw);
+  pdl_wait();
+
+  load_tile_of<DK>(kc, a.nkv, kvh, bt, kstart, lo, hi, base, ps_log2);
+  load_tile_of<DV>(vc, nv, vh, bt, kstart, lo, hi, base + K_BYTES, ps_log2);
+  cp_async_commit();
+
+  const int wrow0 = warp * 16;
+  const int pos0 = first + wrow0 + g, pos1 = pos0 + 8;
+  unsigned qf[DK / 16][4];
+  const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)(t0 + q0 + wrow0) * a.q_stride + (size_t)h * DK;
+  load_q_frags<DK>(qf, [&](int r) { return wrow0 + r < nrows ? qbase + (size_t)r * a.q_stride : nullptr; });
+  const bool row0_ok = wrow0 + g < nrows, row1_ok = wrow0 + g + 8 < nrows;
+  const int wlast = first + min(wrow0 + 15, nrows - 1);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+  const float scale = a.scale, cap = a.softcap;
+
+  for (int it = 0; it < ntiles; ++it) {
+    if (it + 1 < ntiles) {
+      const int st = (it + 1) % STAGES;
+      load_tile_of<DK>(kc, a.nkv, kvh, bt, kstart + (it + 1) * MMA_BK, lo, hi, base + st * STAGE, ps_log2);
+      load_tile_of<DV>(vc, nv, vh, bt, kstart + (it + 1) * MMA_BK, lo, hi, base + st * STAGE + K_BYTES, ps_log2);
+    }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    const int st = it % STAGES;
+    const unsigned ks = base + st * STAGE, vs = ks + K_BYTES;
+    const int kb = kstart + it * MMA_BK;
+    if (wrow0 < nrows && kb <= wlast) {
+      float s[8][4];
+      qk_mma<DK, 8>(qf, ks, 0, s);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tk = kb + j * 8 + c2 + (e & 1);
+          const int pos = (e & 2) ? pos1 : pos0;
+          const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
+                          (a.window <= 0 || tk > pos - a.window);
+          s[j][e] = ok ? score_exp2(s[j][e], scale, cap) : -INFINITY;
+        }
+      }
+      unsigned p[4][4];
+      softmax_update<DV, 8>(s, m, l, o, p);
+      pv_mma<DV, 8>(p, vs, 0, o);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  pdl_trigger();
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  const size_t ostride = (size_t)a.nh * DV;
+  const size_t at0 = (size_t)(t0 + q0 + wrow0 + g) * ostride + (size_t)h * DV, at1 = at0 + 8 * ostride;
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) {
+    const int col = nt * 8 + c2;
+    if (a.out_f32) {
+      float* out = (float*)a.out;
+      if (row0_ok) *reinterpret_cast<float2*>(out + at0 + col) = make_float2(o[nt][0] * inv0, o[nt][1] * inv0);
+      if (row1_ok) *reinterpret_cast<float2*>(out + at1 + col) = make_float2(o[nt][2] * inv1, o[nt][3] * inv1);
+    } else {
+      __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+      if (row0_ok) *reinterpret_cast<unsigned*>(out + at0 + col) = pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+      if (row1_ok) *reinterpret_cast<unsigned*>(out + at1 + col) = pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+    }
+  }
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int K_BYTES = MMA_BK * DK * 2, V_BYTES = MMA_BK * DV * 2, STAGE = K_BYTES + V_BYTES;
+  constexpr int STAGES = 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c2 = (lane & 3) * 2;
+  const int ps_log2 = 31 - __clz(a.page_size);
+  const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
+  const int b = a.dec_seqs[blockIdx.x];
+  const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * 16;
+  const int vsh = a.v_share > 1 ? a.v_share : 1, nv = a.nkv / vsh, vh = kvh / vsh;
+  const int split = blockIdx.z, S = a.num_splits;
+  const int nrows = min(16, G - g0);
+  const int ctx = b >= 0 ? a.context_lens[b] : 0;
+  const int t = b >= 0 ? a.cu_q_lens[b] : 0;
+  const int lo0 = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int n = ctx - lo0;
+  int chunk = (n + S - 1) / S;
+  chunk = ((chunk + MMA_BK - 1) / MMA_BK) * MMA_BK;
+  const int lo = lo0 + split * chunk, hi = min(ctx, lo + chunk);
+  const int head0 = kvh * G + g0;
+  const int* bt = a.block_tables + (size_t)(b >= 0 ? b : 0) * a.bt_stride;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.kcache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.vcache;
+  const unsigned base = smem_u32(smem_raw);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+  const int ntiles = lo < hi ? (hi - lo + MMA_BK - 1) / MMA_BK : 0;
+  pdl_wait();
+  if (ntiles > 0) {
+    load_tile_of<DK>(kc, a.nkv, kvh, bt, lo, lo, hi, base, ps_log2);
+    load_tile_of<DV>(vc, nv, vh, bt, lo, lo, hi, base + K_BYTES, ps_log2);
+    cp_async_commit();
+    unsigned qf[DK / 16][4];
+    const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * DK;
+    load_q_frags<DK>(qf, [&](int r) { return r < nrows ? qbase + (size_t)r * DK : nullptr; });
+    const float scale = a.scale, cap = a.softcap;
+    for (int it = 0; it < ntiles; ++it) {
+      if (it + 1 < ntiles) {
+        const int st = (it + 1) % STAGES;
+        load_tile_of<DK>(kc, a.nkv, kvh, bt, lo + (it + 1) * MMA_BK, lo, hi, base + st * STAGE, ps_log2);
+        load_tile_of<DV>(vc, nv, vh, bt, lo + (it + 1) * MMA_BK, lo, hi, base + st * STAGE + K_BYTES, ps_log2);
+      }
+      cp_async_commit();
+      cp_async_wait<STAGES - 1>();
+      __syncthreads();
+      const int st = it % STAGES;
+      const unsigned ks = base + st * STAGE, vs = ks + K_BYTES;
+      const int key0 = warp * 16;
+      const int tok0 = lo + it * MMA_BK + key0;
+      if (tok0 < hi) {
+        float s[2][4];
+        qk_mma<DK, 2>(qf, ks, key0, s);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int tk = tok0 + j * 8 + c2;
+          s[j][0] = tk < hi ? score_exp2(s[j][0], scale, cap) : -INFINITY;
+          s[j][2] = tk < hi ? score_exp2(s[j][2], scale, cap) : -INFINITY;
+          s[j][1] = tk + 1 < hi ? score_exp2(s[j][1], scale, cap) : -INFINITY;
+          s[j][3] = tk + 1 < hi ? score_exp2(s[j][3], scale, cap) : -INFINITY;
+        }
+        unsigned p[1][4];
+        softmax_update<DV, 2>(s, m, l, o, p);
+        pv_mma<DV, 2>(p, vs, key0, o);
+      }
+      __syncthreads();
+    }
+    cp_async_wait<0>();
+  }
+  pdl_trigger();
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  float* cm = reinterpret_cast<float*>(smem_raw);          // [4][16]
+  float* cl = cm + 64;                                     // [4][16]
+  float* co = cl + 64;                                     // [4][16][DV]
+  __syncthreads();
+  if ((lane & 3) == 0) {
+    cm[warp * 16 + g] = m[0]; cm[warp * 16 + g + 8] = m[1];
+    cl[warp * 16 + g] = l[0]; cl[warp * 16 + g + 8] = l[1];
+  }
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) {
+    float* r0 = co + ((size_t)warp * 16 + g) * DV + nt * 8 + c2;
+    float* r1 = co + ((size_t)warp * 16 + g + 8) * DV + nt * 8 + c2;
+    r0[0] = o[nt][0]; r0[1] = o[nt][1];
+    r1[0] = o[nt][2]; r1[1] = o[nt][3];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < nrows * DV; e += MMA_THREADS) {
+    const int r = e / DV, col = e - r * DV;
+    const float M = fmaxf(fmaxf(cm[r], cm[16 + r]), fmaxf(cm[32 + r], cm[48 + r]));
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = cm[w * 16 + r];
+      if (mw != -INFINITY) {
+        const float f = fast_exp2(mw - M);
+        L += f * cl[w * 16 + r];
+        acc += f * co[((size_t)w * 16 + r) * DV + col];
+      }
+    }
+    const size_t row = ((size_t)blockIdx.x * a.nh + head0 + r) * S + split;
+    a.part_o[row * DV + col] = acc;
+    if (col == 0) {
+      a.part_ml[row * 2] = M == -INFINITY ? -INFINITY : M * (1.0f / LOG2E);     // the merge kernel works in base e
+      a.part_ml[row * 2 + 1] = L;
+    }
+  }
+}
+
+bool attn_mma_x_supported(int dtype, int d, int dv, int page_size) {
+  return dtype == GG_BF16 && (d == 64 || d == 128) && (dv == 64 || dv == 128) && power_of_two(page_size);
+}
+
+template <int DK, int DV>
+static int prefill_x_go(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * MMA_BK * (DK + DV) * 2;
+  int rc = opt_in_smem(attn_prefill_mma_x_kernel<DK, DV>, smem, "attn_prefill_x");
+  if (rc) return rc;
+  gg_launch(attn_prefill_mma_x_kernel<DK, DV>, dim3(num_tiles, a.nh), dim3(MMA_THREADS), smem, stream, a);
+  return gg_check_launch("attn_prefill_x");
+}
+
+int attn_prefill_mma_x(const AttnArgs& a, int num_tiles, cudaStream_t stream) {
+  GG_REQUIRE(num_tiles >= 0 && a.nh <= 65535, "attn_prefill_x: bad grid");
+  if (num_tiles == 0) return GG_OK;
+  const int dv = a.dv > 0 ? a.dv : a.d;
+  if (a.d == 64 && dv == 64) return prefill_x_go<64, 64>(a, num_tiles, stream);
+  if (a.d == 64 && dv == 128) return prefill_x_go<64, 128>(a, num_tiles, stream);
+  if (a.d == 128 && dv == 64) return prefill_x_go<128, 64>(a, num_tiles, stream);
+  return prefill_x_go<128, 128>(a, num_tiles, stream);
+}
+
+template <int DK, int DV>
+static int decode_x_go(const AttnArgs& a, int n_dec, cudaStream_t stream) {
+  size_t smem = (size_t)2 * MMA_BK * (DK + DV) * 2;
+  const size_t combine = (size_t)(128 + 4 * 16 * DV) * sizeof(float);
+  if (combine > smem) smem = combine;
+  int rc = opt_in_smem(attn_decode_mma_x_kernel<DK, DV>, smem, "attn_decode_x");
+  if (rc) return rc;
+  const int G = a.nh / a.nkv, gchunks = (G + 15) / 16;
+  GG_REQUIRE(a.nkv * gchunks <= 65535 && a.num_splits <= 65535, "attn_decode_x: too many heads or slices");
+  gg_launch(attn_decode_mma_x_kernel<DK, DV>, dim3(n_dec, a.nkv * gchunks, a.num_splits), dim3(MMA_THREADS), smem, stream, a);
+  return gg_check_launch("attn_decode_x");
+}
+
+int attn_decode_mma_x(const AttnArgs& a, int n_dec, cudaStream_t stream) {
+  const int dv = a.dv > 0 ? a.dv : a.d;
+  if (a.d == 64 && dv == 64) return decode_x_go<64, 64>(a, n_dec, stream);
+  if (a.d == 64 && dv == 128) return decode_x_go<64, 128>(a, n_dec, stream);
+  if (a.d == 128 && dv == 64) return decode_x_go<128, 64>(a, n_dec, stream);
+  return decode_x_go<128, 128>(a, n_dec, stream);
+}

@@ -7,11 +7,11 @@
 //
 // Three kernels a step, every one for any mix of prompt portions and single decoded tokens:
 //   delta_prep     per (token, head unit): convolution + SiLU, unit norms, beta and decay
-//   delta_recur    per (sequence, head, 32 value columns): the recurrence over the portion
+//   delta_recur    per (sequence, head, 16 value columns): the recurrence over the portion
 //   delta_out      per (token, head): o / rms(o) * weight * silu(gate)
 // and delta_conv_state, which moves the convolution's window on after delta_prep has read it.
 // Every column j of S evolves on its own (S[:, j] only ever meets v_j and u_j), so the columns
-// of a head are spread over CTAs; four lanes share a column and split its d rows.
+// of a head are spread over CTAs; eight lanes share a column and split its d rows.
 // Everything here is float32 arithmetic; only the projections that come in (x, gate) and the
 // result that goes out are in the activation type.
 #include "common.cuh"
@@ -114,11 +114,19 @@ __global__ void delta_conv_state_kernel(const TA* __restrict__ x, long long x_st
 }
 
 // ---------------------------------------------------------------- the recurrence
-#define DR_COLS 32          // value columns of one CTA
-#define DR_LANES 4          // lanes that share a column
+#define DR_COLS 16          // value columns of one CTA
+#define DR_LANES 8          // lanes that share a column: lane r holds rows r, r + 8, r + 16, ... of it
 #define DR_CHUNK 16         // tokens staged in shared memory at a time
+#define DR_STAGE_FLOATS(dp) (2 * DR_CHUNK * (dp) + DR_CHUNK * DR_COLS + 2 * DR_CHUNK)
 
-// grid (B, H, ceil(dv / 32)), 128 threads.  state [slots, H, dv, d].
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// grid (B, H, ceil(dv / 16)), 128 threads.  state [slots, H, dv, d].
 template <int DPT>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
@@ -127,7 +135,7 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
   extern __shared__ float sm[];
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
-  const int tid = threadIdx.x, r = tid & (DR_LANES - 1), cl = tid >> 2, col = col0 + cl;
+  const int tid = threadIdx.x, r = tid & (DR_LANES - 1), cl = tid / DR_LANES, col = col0 + cl;
   const int C = 2 * G * d + H * dv;
   const int slot = state_slots[b];
   const int t0 = cu_q_lens[b], qlen = cu_q_lens[b + 1] - t0;
@@ -135,56 +143,99 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
   const int start = context_lens[b] - qlen;
   const int kvh = h / (H / G);
   const int dp = DPT * DR_LANES;                 // d rounded up to what the lanes hold
-  float* ks = sm;                                // [CHUNK][dp]
-  float* qs = ks + DR_CHUNK * dp;                // [CHUNK][dp]
-  float* vs = qs + DR_CHUNK * dp;                // [CHUNK][COLS]
-  float* bg = vs + DR_CHUNK * DR_COLS;           // [CHUNK][2]
-  float* os = bg + DR_CHUNK * 2;                 // [CHUNK][COLS]
+  float* ks = sm;                                // two stages of k [CHUNK][dp], q [CHUNK][dp], v [CHUNK][COLS], (beta, decay) [CHUNK][2]
+  float* os = sm + 2 * DR_STAGE_FLOATS(dp);      // [CHUNK][COLS]
   const bool live = col < dv;
   float S[DPT];
   float* srow = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
-    const int row = r * DPT + i;
+    const int row = i * DR_LANES + r;
     S[i] = (live && start > 0 && row < d) ? srow[row] : 0.f;
   }
   pdl_wait();
-  for (int c0 = 0; c0 < qlen; c0 += DR_CHUNK) {
+  // A chunk's rows come to shared memory by asynchronous copies, the next chunk's while this one
+  // is worked on (plain loads issued in a loop went out one after the other and cost more than
+  // the recurrence itself).  16-byte copies where every row starts on such a border.
+  const bool vec = (d & 3) == 0 && (dv & 3) == 0;
+  auto stage = [&](int c0, int buf) {
     const int n = min(DR_CHUNK, qlen - c0);
-    __syncthreads();
-    for (int e = tid; e < n * dp; e += blockDim.x) {
-      const int tt = e / dp, row = e - tt * dp;
-      const size_t base = (size_t)(t0 + c0 + tt) * C;
-      ks[e] = row < d ? qkv[base + (size_t)(G + kvh) * d + row] : 0.f;
-      qs[e] = row < d ? qkv[base + (size_t)kvh * d + row] : 0.f;
-    }
-    for (int e = tid; e < n * DR_COLS; e += blockDim.x) {
-      const int tt = e / DR_COLS, cc = e - tt * DR_COLS;
-      vs[e] = col0 + cc < dv ? qkv[(size_t)(t0 + c0 + tt) * C + 2 * G * d + (size_t)h * dv + col0 + cc] : 0.f;
+    float* kb = ks + buf * DR_STAGE_FLOATS(dp);
+    float* qb = kb + DR_CHUNK * dp;
+    float* vb = qb + DR_CHUNK * dp;
+    float* gb = vb + DR_CHUNK * DR_COLS;
+    if (vec) {
+      const int per = dp >> 2;
+      for (int e = tid; e < n * per; e += blockDim.x) {
+        const int tt = e / per, row = (e - tt * per) << 2;
+        const float* src = qkv + (size_t)(t0 + c0 + tt) * C;
+        const int bytes = row < d ? 16 : 0;
+        dr_cp16(kb + tt * dp + row, src + (size_t)(G + kvh) * d + (bytes ? row : 0), bytes);
+        dr_cp16(qb + tt * dp + row, src + (size_t)kvh * d + (bytes ? row : 0), bytes);
+      }
+      for (int e = tid; e < n * (DR_COLS / 4); e += blockDim.x) {
+        const int tt = e / (DR_COLS / 4), cc = (e - tt * (DR_COLS / 4)) << 2;
+        const int bytes = col0 + cc < dv ? 16 : 0;
+        dr_cp16(vb + tt * DR_COLS + cc, qkv + (size_t)(t0 + c0 + tt) * C + 2 * G * d + (size_t)h * dv + (bytes ? col0 + cc : 0), bytes);
+      }
+    } else {
+      for (int e = tid; e < n * dp; e += blockDim.x) {
+        const int tt = e / dp, row = e - tt * dp;
+        const size_t base = (size_t)(t0 + c0 + tt) * C;
+        kb[e] = row < d ? qkv[base + (size_t)(G + kvh) * d + row] : 0.f;
+        qb[e] = row < d ? qkv[base + (size_t)kvh * d + row] : 0.f;
+      }
+      for (int e = tid; e < n * DR_COLS; e += blockDim.x) {
+        const int tt = e / DR_COLS, cc = e - tt * DR_COLS;
+        vb[e] = col0 + cc < dv ? qkv[(size_t)(t0 + c0 + tt) * C + 2 * G * d + (size_t)h * dv + col0 + cc] : 0.f;
+      }
     }
     if (tid < n) {
-      bg[tid * 2] = beta[(size_t)(t0 + c0 + tid) * H + h];
-      bg[tid * 2 + 1] = decay[(size_t)(t0 + c0 + tid) * H + h];
+      dr_cp4(gb + tid * 2, beta + (size_t)(t0 + c0 + tid) * H + h);
+      dr_cp4(gb + tid * 2 + 1, decay + (size_t)(t0 + c0 + tid) * H + h);
     }
+  };
+  stage(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int c0 = 0, buf = 0; c0 < qlen; c0 += DR_CHUNK, buf ^= 1) {
+    const int n = min(DR_CHUNK, qlen - c0);
+    if (c0 + DR_CHUNK < qlen) stage(c0 + DR_CHUNK, buf ^ 1);       // the buffer the chunk before last was read from
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
+    const float* kc = ks + buf * DR_STAGE_FLOATS(dp);
+    const float* qc = kc + DR_CHUNK * dp;
+    const float* vcur = qc + DR_CHUNK * dp;
+    const float* bg = vcur + DR_CHUNK * DR_COLS;
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      const float* kr = ks + tt * dp + r * DPT;
-      const float* qr = qs + tt * dp + r * DPT;
+      // lane r reads rows r, r + 8, ...: neighbouring lanes read neighbouring words (no bank
+      // conflicts), and the sums run in four chains so that the additions overlap
+      const float* kr = kc + tt * dp + r;
+      const float* qr = qc + tt * dp + r;
       const float be = bg[tt * 2], g = bg[tt * 2 + 1];
-      float dot = 0.f;
-#pragma unroll
-      for (int i = 0; i < DPT; ++i) dot = fmaf(kr[i], S[i], dot);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      const float u = be * (vs[tt * DR_COLS + cl] - g * dot);
-      float o = 0.f;
+      float kv[DPT];
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
-        S[i] = fmaf(kr[i], u, g * S[i]);
-        o = fmaf(qr[i], S[i], o);
+        kv[i] = kr[i * DR_LANES];
+        d4[i & 3] = fmaf(kv[i], S[i], d4[i & 3]);
       }
+      float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      const float u = be * (vcur[tt * DR_COLS + cl] - g * dot);
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        S[i] = fmaf(kv[i], u, g * S[i]);
+        o4[i & 3] = fmaf(qr[i * DR_LANES], S[i], o4[i & 3]);
+      }
+      float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
       if (r == 0) os[tt * DR_COLS + cl] = o;
     }
     __syncthreads();
@@ -193,10 +244,11 @@ delta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ beta
       if (col0 + cc < dv) o_raw[(size_t)(t0 + c0 + tt) * H * dv + (size_t)h * dv + col0 + cc] = os[e];
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (live) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-      const int row = r * DPT + i;
+      const int row = i * DR_LANES + r;
       if (row < d) srow[row] = S[i];
     }
   }
@@ -257,7 +309,7 @@ static int delta_recur_launch(const float* qkv, const float* beta, const float* 
                               const int* cu_q_lens, const int* context_lens, const int* state_slots, int B, int G, int H,
                               int d, int dv, float* o_raw, cudaStream_t stream) {
   const int dp = DPT * DR_LANES;
-  const size_t smem = (size_t)(2 * DR_CHUNK * dp + 2 * DR_CHUNK * DR_COLS + 2 * DR_CHUNK) * sizeof(float);
+  const size_t smem = (size_t)(2 * DR_STAGE_FLOATS(dp) + DR_CHUNK * DR_COLS) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recur_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gg_fail(GG_ERR_CUDA, "delta_recur: %s", cudaGetErrorString(e));
@@ -275,11 +327,11 @@ extern "C" int gg_delta_recur(const float* qkv, const float* beta, const float* 
   GG_REQUIRE(d <= 256, "delta_recur: key size %d is beyond 256", d);
   GG_REQUIRE(H <= 65535 && (dv + DR_COLS - 1) / DR_COLS <= 65535, "delta_recur: too many heads or columns");
 #define DR_GO(N) return delta_recur_launch<N>(qkv, beta, decay, state, cu_q_lens, context_lens, state_slots, B, G, H, d, dv, o_raw, stream)
-  if (d <= 16) DR_GO(4);
-  if (d <= 32) DR_GO(8);
-  if (d <= 64) DR_GO(16);
-  if (d <= 128) DR_GO(32);
-  DR_GO(64);
+  if (d <= 16) DR_GO(2);
+  if (d <= 32) DR_GO(4);
+  if (d <= 64) DR_GO(8);
+  if (d <= 128) DR_GO(16);
+  DR_GO(32);
 #undef DR_GO
 }
 

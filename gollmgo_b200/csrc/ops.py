@@ -691,13 +691,17 @@ def rope_kv_write_x(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Op
 def attn_prefill_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                    block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
                    tile_seq: torch.Tensor, tile_q0: torch.Tensor, num_tiles: int, out: torch.Tensor, nh: int, nkv: int,
-                   d: int, dv: int, v_share: int, page_size: int, window: int, scale: float, softcap: float) -> None:
-    """Causal attention of prompt portions (tiles of 16 queries) with keys of size d, values of
-    size dv, ``v_share`` key heads to a value head, optional window and capped scores; out
-    [T, nh*dv] in the cache's type or float32."""
+                   d: int, dv: int, v_share: int, page_size: int, window: int, scale: float, softcap: float,
+                   tile64_seq: Optional[torch.Tensor] = None, tile64_q0: Optional[torch.Tensor] = None,
+                   num_tiles64: int = 0, allow_mma: bool = True) -> None:
+    """Causal attention of prompt portions with keys of size d, values of size dv, ``v_share`` key
+    heads to a value head, optional window and capped scores; out [T, nh*dv] in the cache's type or
+    float32.  ``tile_*`` list tiles of 16 queries (general kernel, float32 arithmetic), ``tile64_*``
+    of 64 (mma.sync kernel: bfloat16, d and dv 64 or 128)."""
     _check(lib().gg_attn_prefill_x(_p(q), ctypes.c_longlong(q_stride), _p(kcache), _p(vcache), dtype_code(kcache.dtype),
                                    _p(block_tables), bt_stride, _p(cu_q_lens), _p(context_lens), _p(tile_seq),
-                                   _p(tile_q0), num_tiles, _p(out), int(out.dtype == torch.float32 and kcache.dtype != torch.float32),
+                                   _p(tile_q0), num_tiles, _p(tile64_seq), _p(tile64_q0), num_tiles64, int(allow_mma),
+                                   _p(out), int(out.dtype == torch.float32 and kcache.dtype != torch.float32),
                                    nh, nkv, d, dv, v_share, page_size, window, ctypes.c_float(scale),
                                    ctypes.c_float(softcap), _stream()))
 
@@ -706,7 +710,7 @@ def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: 
                   block_tables: torch.Tensor, bt_stride: int, cu_q_lens: torch.Tensor, context_lens: torch.Tensor,
                   dec_seqs: torch.Tensor, n_dec: int, num_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor,
                   out: torch.Tensor, nh: int, nkv: int, d: int, dv: int, v_share: int, page_size: int, window: int,
-                  scale: float, softcap: float) -> None:
+                  scale: float, softcap: float, allow_mma: bool = True) -> None:
     """The same for single decoded tokens, split over the context and merged."""
     if part_o.numel() < n_dec * nh * num_splits * dv or part_ml.numel() < n_dec * nh * num_splits * 2:
         raise KernelError("attn_decode_x: scratch too small")
@@ -715,7 +719,7 @@ def attn_decode_x(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: 
                                   num_splits, _p(part_o), _p(part_ml), _p(out),
                                   int(out.dtype == torch.float32 and kcache.dtype != torch.float32), nh, nkv, d, dv,
                                   v_share, page_size, window, ctypes.c_float(scale), ctypes.c_float(softcap),
-                                  _stream()), 2)
+                                  int(allow_mma), _stream()), 2)
 
 
 def diff_combine(maps: torch.Tensor, out: torch.Tensor, lam: float, eps: float, post: float, heads: int,

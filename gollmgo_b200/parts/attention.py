@@ -147,6 +147,9 @@ class Attention:
         self.qkv_width = (self.nh + self.nkv) * self.d + self.nv * self.dv
         self.qkv_bias = None
         self.o_bias = None
+        # the general path on mma.sync: bfloat16, keys and values of 64 or 128
+        self._mma_x = (self.general and ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and self.dv in (64, 128)
+                       and ATTN_POLICY != "general" and self.qkv_width % 8 == 0)
         self.num_sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count \
             if ctx.device.type == "cuda" else 148
         ws, T = ctx.workspace, ctx.max_tokens
@@ -185,6 +188,8 @@ class Attention:
         """The tile lists of the prompt kernels this mixer can end up using."""
         need = [TILES_GENERAL]
         if self.general:
+            if self._mma_x:
+                need.append(TILES_MMA)
             return need
         if self.ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and ATTN_POLICY != "general":
             need.append(TILES_MMA)
@@ -286,10 +291,12 @@ class Attention:
             if TILES_GENERAL not in batch.tiles:
                 raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
                                    "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
-            t16 = batch.tiles[TILES_GENERAL]
+            t16, t64 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA) if self._mma_x else None
             ops.attn_prefill_x(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                                t16.seq, t16.q0, t16.count, out, self.nh, self.nkv, self.d, self.dv, self.v_share,
-                               self.ctx.page_size, window, self.scale, self.softcap)
+                               self.ctx.page_size, window, self.scale, self.softcap,
+                               t64.seq if t64 else None, t64.q0 if t64 else None, t64.count if t64 else 0,
+                               allow_mma=t64 is not None)
         if batch.num_decode:
             n = batch.num_decode
             facts = getattr(batch, "facts", None)
@@ -298,7 +305,8 @@ class Attention:
             ops.attn_decode_x(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                               batch.dec_seqs, n, splits, ws.get("attn_part_o", 1, n * self.nh * splits * self.dv),
                               ws.get("attn_part_ml", 1, n * self.nh * splits * 2), out, self.nh, self.nkv, self.d,
-                              self.dv, self.v_share, self.ctx.page_size, window, self.scale, self.softcap)
+                              self.dv, self.v_share, self.ctx.page_size, window, self.scale, self.softcap,
+                              allow_mma=self._mma_x)
         return out
 
     def forward(self, x, batch, cache, writes_cache=True, then=None):
