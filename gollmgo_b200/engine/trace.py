@@ -27,14 +27,17 @@ PAGE_ROUND = 64          # a request's token count is rounded up to this in --ma
 
 
 def make_trace_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 16,
-                      max_live: int = 4, token_budget: int = 8192, cuda_graphs: bool = True) -> ModelRunner:
+                      max_live: int = 4, token_budget: int = 8192, cuda_graphs: bool = True,
+                      state_slots: int = None) -> ModelRunner:
+    """``state_slots``: how many requests can be admitted at once (each holds a state slot that is
+    used again when it ends); None = the engine's default for the batch size."""
     if PAGE_ROUND % block_size:
         raise ValueError(f"page size {block_size} does not divide {PAGE_ROUND}")
     max_tokens = max(PAGE_ROUND, -(-max_tokens // PAGE_ROUND) * PAGE_ROUND)
     ecfg = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=max_tokens // block_size,
                         max_batch_size=max(2 * max_live, 8),
                         max_token_budget=min(token_budget, max_tokens),
-                        max_model_len=max_tokens, cuda_graphs=cuda_graphs, state_slots=max_live)
+                        max_model_len=max_tokens, cuda_graphs=cuda_graphs, state_slots=state_slots)
     return ModelRunner(read_config_json(model_dir), ecfg, weights=model_dir)
 
 
