@@ -29,7 +29,8 @@ def _mixer(cfg: BevuvikConfig, m) -> PartSpec:
         return PartSpec("diff_attention", {"hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads,
                                            "head_dim": m.dim, "v_head_dim": m.vdim, "window": m.window,
                                            "position": _position(m.rot, m.dim, True), "scale": m.scale, "diff": m.diff,
-                                           "eps": cfg.eps, "biases": True, "names": names})
+                                           "eps": cfg.eps, "biases": True, "names": names,
+                                           "defer_output_bias": True})      # the parallel block adds it with the stream
     left, right = m.left, m.right
     attn = PartSpec("attention", {"hidden_size": cfg.width, "num_heads": left.heads, "num_kv_heads": left.kv_heads,
                                   "head_dim": left.dim, "v_head_dim": left.vdim, "window": left.window,

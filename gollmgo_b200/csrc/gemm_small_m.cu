@@ -41,6 +41,9 @@ struct GsmFuse {
   float* resid;               // GSM_OUT_RESNORM: [M, N] float32 residual stream, updated in place
   const float* norm_w;        // [N] weight of the norm that follows
   float* out_partials;        // [tiles of 16 columns, 16]
+  // the gated product's activation: limit <= 0: silu(gate) * up; limit > 0: with g = min(gate, limit)
+  // and u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + shift)
+  float act_limit, act_alpha, act_shift;
 };
 
 #define GSM_STAGES 6
@@ -219,7 +222,14 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 #pragma unroll
               for (int wv = 0; wv < GSM_WARPS; ++wv) { gate += red[wv][r][tok]; up += red[wv][r + 8][tok]; }
               if (fuse.in_partials) { gate *= row_scale[tok]; up *= row_scale[tok]; }
-              const float v = gate / (1.f + expf(-gate)) * up;
+              float v;
+              if (fuse.act_limit > 0.f) {
+                const float gl = fminf(gate, fuse.act_limit);
+                const float ul = fminf(fmaxf(up, -fuse.act_limit), fuse.act_limit);
+                v = gl / (1.f + expf(-fuse.act_alpha * gl)) * (ul + fuse.act_shift);
+              } else {
+                v = gate / (1.f + expf(-gate)) * up;
+              }
               reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * N + f] = __float2bfloat16_rn(v);
             }
           }
@@ -270,10 +280,10 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 // up rows) and out is bfloat16 [M, N] = silu(x Wg^T) * (x Wu^T); 3 = out is the bfloat16
 // input of the next norm and resid / norm_w / out_partials are used (see GsmFuse).
 // in_partials (or null) with in_tiles, hidden and eps: x is an unnormalised norm input.
-extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W, void* out, int M, int N,
-                                     int K, int mode, const float* in_partials, int in_tiles, int hidden,
-                                     float eps, float* resid, const float* norm_w, float* out_partials,
-                                     cudaStream_t stream) {
+static int gemm_small_m_run(const void* x, long long ldx, const void* W, void* out, int M, int N,
+                            int K, int mode, const float* in_partials, int in_tiles, int hidden,
+                            float eps, float* resid, const float* norm_w, float* out_partials,
+                            float act_limit, float act_alpha, float act_shift, cudaStream_t stream) {
   GG_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_small_m: bad sizes M=%d N=%d K=%d", M, N, K);
   GG_REQUIRE(M <= 16, "gemm_small_m: %d tokens; this kernel takes at most 16", M);
   GG_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_small_m: K=%d and the row stride %lld of x must be multiples of 8", K, ldx);
@@ -286,6 +296,7 @@ extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W
   fuse.in_partials = in_partials; fuse.in_tiles = in_tiles;
   fuse.inv_h = hidden > 0 ? 1.0f / (float)hidden : 0.f; fuse.eps = eps;
   fuse.resid = resid; fuse.norm_w = norm_w; fuse.out_partials = out_partials;
+  fuse.act_limit = act_limit; fuse.act_alpha = act_alpha; fuse.act_shift = act_shift;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
   const int num_tiles = mode == GSM_OUT_SILU ? (N + 7) / 8 : (N + 15) / 16;
@@ -325,6 +336,22 @@ extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W
 #undef GSM_MODES
 #undef GSM_LAUNCH
   return gg_check_launch("gemm_small_m");
+}
+
+extern "C" int gg_gemm_small_m_fused(const void* x, long long ldx, const void* W, void* out, int M, int N,
+                                     int K, int mode, const float* in_partials, int in_tiles, int hidden,
+                                     float eps, float* resid, const float* norm_w, float* out_partials,
+                                     cudaStream_t stream) {
+  return gemm_small_m_run(x, ldx, W, out, M, N, K, mode, in_partials, in_tiles, hidden, eps, resid, norm_w, out_partials,
+                          0.f, 0.f, 0.f, stream);
+}
+
+// The gated product (mode 2) with the clamped activation: out = g * sigmoid(alpha * g) * (u + shift),
+// g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit); limit > 0.
+extern "C" int gg_gemm_small_m_clamped(const void* x, long long ldx, const void* W, void* out, int M, int N, int K,
+                                       float limit, float alpha, float shift, cudaStream_t stream) {
+  GG_REQUIRE(limit > 0.f, "gemm_small_m: the clamped activation needs a positive limit");
+  return gemm_small_m_run(x, ldx, W, out, M, N, K, 2, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, limit, alpha, shift, stream);
 }
 
 extern "C" int gg_gemm_small_m(const void* x, long long ldx, const void* W, void* out, int M, int N,

@@ -344,6 +344,20 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: boo
                                        _p(resid), _p(norm_w), _p(out_partials), _stream()))
 
 
+def gemm_small_m_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, limit: float, alpha: float,
+                         shift: float) -> None:
+    """The gated product of gemm_small_m (w [2N, K]: gate rows, then up rows) with the clamped
+    activation in its epilogue: out = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit),
+    u = clamp(up, -limit, limit); bfloat16, M <= 16."""
+    M, K = x.shape
+    N = out.shape[1]
+    if w.shape != (2 * N, K) or out.shape[0] != M or not out.is_contiguous() or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_small_m_clamped: shapes do not fit")
+    _cuda(w, out)
+    _check(lib().gg_gemm_small_m_clamped(_p(x), ctypes.c_longlong(x.stride(0)), _p(w), _p(out), M, N, K,
+                                         ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(shift), _stream()))
+
+
 _TC_STATUS = {}
 tc_launched = False       # a tcgen05 product was launched since the status word was last checked
 

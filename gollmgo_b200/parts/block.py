@@ -147,7 +147,8 @@ class PostNormBlock:
 class ParallelBlock:
     """x += mult * (mixer(h) + ff(h)) with h = norm(x): one norm, and both sublayers read its
     output.  A layer without a feed-forward adds the mixer alone.  params: residual_mult (default 1).
-    The sum of the sublayers and the add to the stream are float32 (one kernel)."""
+    The sum of the sublayers and the add to the stream are float32 (one kernel); a mixer that leaves
+    the bias of its output projection in ``deferred_bias`` has it added by the same kernel."""
 
     def __init__(self, layer_spec, mixer, feed_forward, mixer_norm, ffn_norm, ctx):
         self.mixer, self.feed_forward, self.mixer_norm, self.ctx = mixer, feed_forward, mixer_norm, ctx
@@ -167,7 +168,7 @@ class ParallelBlock:
         self.mixer_norm.add_norm(resid, delta, h)
         a = self.mixer.forward(h, batch, cache, writes_cache)
         f = self.feed_forward.forward(h, batch) if self.feed_forward is not None else None
-        ops.scaled_add(resid, a, f, self.mult)
+        ops.scaled_add(resid, a, f, self.mult, getattr(self.mixer, "deferred_bias", None))
         return None
 
 

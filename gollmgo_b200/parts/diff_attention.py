@@ -14,7 +14,9 @@ reordered at load time from [head][map] to [kv group][map][head in group]; the k
 combines the maps reads them in that order and writes heads in the checkpoint's order.
 
 params: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, window, position (PartSpec),
-scale, diff, eps, biases (bool), names (q, k, v, o), lambda_names (lq1, lk1, lq2, lk2), out_buffer.
+scale, diff, eps, biases (bool), names (q, k, v, o), lambda_names (lq1, lk1, lq2, lk2), out_buffer,
+defer_output_bias (bool: the output projection's bias is not added here but left in ``deferred_bias``
+for a block that adds the mixer's result to the stream with a kernel that takes a bias).
 """
 from __future__ import annotations
 
@@ -37,6 +39,8 @@ class DiffAttention(Attention):
         self.diff = float(spec["diff"])
         self.eps = float(spec["eps"])
         self.lambda_names = tuple(spec.get("lambda_names") or ("lq1", "lk1", "lq2", "lk2"))
+        self.defer_output_bias = bool(spec.get("defer_output_bias", False))
+        self.deferred_bias = None
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} heads are not a multiple of {self.kv_heads} kv heads")
         # the maps as heads: twice the heads on twice the key heads
@@ -76,6 +80,8 @@ class DiffAttention(Attention):
             self.qkv_bias = torch.cat([self._by_group(get(qn + ".b")).float(), get(kn + ".b").float(),
                                        get(vn + ".b").float()]).contiguous()
             self.o_bias = get(on + ".b").float().contiguous()
+            if self.defer_output_bias:
+                self.deferred_bias = self.o_bias
         lq1, lk1, lq2, lk2 = (get(n).double() for n in self.lambda_names)
         self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + self.diff)
 
@@ -92,7 +98,7 @@ class DiffAttention(Attention):
         heads = ws.get("diff_heads", T, self.heads * self.dv)
         ops.diff_combine(maps, heads, self.lam, self.eps, 1.0 - self.diff, self.heads, self.kv_heads, self.dv)
         y = linear(heads, self.w_o, ws.get(self.out_buffer, T, self.hidden))
-        if self.o_bias is not None:
+        if self.o_bias is not None and not self.defer_output_bias:
             ops.bias_add(y, self.o_bias)
         return y
 

@@ -63,8 +63,11 @@ class GatedMLP:
         ws = self.ctx.workspace
         a = ws.get("ffn_act", T, self.inter)
         if self.activation == "clamped_swish":
-            gu = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.inter))
-            ops.clamped_gate(gu, a, self.limit, self.alpha, self.shift)
+            if self.limit > 0 and ops.small_m_ok(x, self.w_gate_up):
+                ops.gemm_small_m_clamped(x, self.w_gate_up, a, self.limit, self.alpha, self.shift)   # product and activation in one
+            else:
+                gu = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.inter))
+                ops.clamped_gate(gu, a, self.limit, self.alpha, self.shift)
         elif isinstance(x, NormedRows):
             ops.gemm_small_m(x.scaled, self.w_gate_up, a, gated=True, in_partials=x.partials,
                              hidden=x.hidden, eps=x.eps)

@@ -130,6 +130,12 @@ class DecoderModel:
                     add(v)
                 elif depth < 2 and hasattr(v, "weights") and hasattr(v, "load"):     # a part inside a part
                     add_part(v, depth + 1)
+                elif depth < 2 and isinstance(v, (list, tuple)):                     # ... or parts and tensors in a list
+                    for item in v:
+                        if isinstance(item, torch.Tensor) and item.dim() >= 1 and item.is_cuda:
+                            add(item)
+                        elif hasattr(item, "weights") and hasattr(item, "load"):
+                            add_part(item, depth + 1)
         add_part(self.final_norm)
         for parts, block in zip(self.parts, self.blocks):
             for part in parts:

@@ -21,7 +21,8 @@ position        cls(spec, ctx)
                   .weights(), .load(get)                      its tensors, under ModelSpec.embed_position_prefix
                   .add_to_embedding(resid, batch)             resid [T, hidden] float32, in place
 mixer           cls(spec, ctx)
-                  .cache_need() -> PagedKVNeed | FixedStateNeed | None
+                  .cache_need() -> PagedKVNeed | FixedStateNeed | None, or a tuple of these (of tuples):
+                                                              ``cache`` in forward is then the tuple of their views
                   .weights(), .load(get)
                   .forward(x, batch, cache, writes_cache) -> tensor [T, hidden]
                   .query_tiles() -> [QueryTiles]              optional: index lists over the query rows of
