@@ -1051,11 +1051,11 @@ __device__ __forceinline__ void load_tile_of(const __nv_bfloat16* cache, int hea
 // score (raw dot product) -> base-2 exponent: scaled, capped where the cap is positive
 // (the hyperbolic tangent is the special-function unit's, like the exponentials of these kernels: one
 // instruction a score, relative error 2^-11, below what rounding the weights to bfloat16 costs)
-__device__ __forceinline__ float score_exp2(float dot, float scale, float cap) {
+__device__ __forceinline__ float score_exp2(float dot, float scale, float cap, float inv_cap) {
   float x = dot * scale;
   if (cap > 0.f) {
     float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(x / cap));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(x * inv_cap));
     x = cap * th;
   }
   return x * LOG2E;
@@ -1102,7 +1102,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
   float o[DV / 8][4];
 #pragma unroll
   for (int nt = 0; nt < DV / 8; ++nt) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
-  const float scale = a.scale, cap = a.softcap;
+  const float scale = a.scale, cap = a.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
 
   for (int it = 0; it < ntiles; ++it) {
     if (it + 1 < ntiles) {
@@ -1127,7 +1127,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_prefill_mma_x_kernel(AttnArg
           const int pos = (e & 2) ? pos1 : pos0;
           const bool ok = ((e & 2) ? row1_ok : row0_ok) && tk >= lo && tk <= pos &&
                           (a.window <= 0 || tk > pos - a.window);
-          s[j][e] = ok ? score_exp2(s[j][e], scale, cap) : -INFINITY;
+          s[j][e] = ok ? score_exp2(s[j][e], scale, cap, inv_cap) : -INFINITY;
         }
       }
       unsigned p[4][4];
@@ -1199,7 +1199,7 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
     unsigned qf[DK / 16][4];
     const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q + (size_t)t * a.q_stride + (size_t)head0 * DK;
     load_q_frags<DK>(qf, [&](int r) { return r < nrows ? qbase + (size_t)r * DK : nullptr; });
-    const float scale = a.scale, cap = a.softcap;
+    const float scale = a.scale, cap = a.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
     for (int it = 0; it < ntiles; ++it) {
       if (it + 1 < ntiles) {
         const int st = (it + 1) % STAGES;
@@ -1219,10 +1219,10 @@ __global__ void __launch_bounds__(MMA_THREADS) attn_decode_mma_x_kernel(AttnArgs
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int tk = tok0 + j * 8 + c2;
-          s[j][0] = tk < hi ? score_exp2(s[j][0], scale, cap) : -INFINITY;
-          s[j][2] = tk < hi ? score_exp2(s[j][2], scale, cap) : -INFINITY;
-          s[j][1] = tk + 1 < hi ? score_exp2(s[j][1], scale, cap) : -INFINITY;
-          s[j][3] = tk + 1 < hi ? score_exp2(s[j][3], scale, cap) : -INFINITY;
+          s[j][0] = tk < hi ? score_exp2(s[j][0], scale, cap, inv_cap) : -INFINITY;
+          s[j][2] = tk < hi ? score_exp2(s[j][2], scale, cap, inv_cap) : -INFINITY;
+          s[j][1] = tk + 1 < hi ? score_exp2(s[j][1], scale, cap, inv_cap) : -INFINITY;
+          s[j][3] = tk + 1 < hi ? score_exp2(s[j][3], scale, cap, inv_cap) : -INFINITY;
         }
         unsigned p[1][4];
         softmax_update<DV, 2>(s, m, l, o, p);

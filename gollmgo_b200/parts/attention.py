@@ -37,6 +37,9 @@ MAX_SPLITS = 16
 # tiles of 16 rows (general kernel, csrc/attention.cu), of 64 (mma.sync, csrc/attention_mma.cu),
 # of 128 with the tiles that attend to most keys first (tcgen05, csrc/attention_tc.cu)
 TILES_GENERAL, TILES_MMA, TILES_TC = QueryTiles(16), QueryTiles(64), QueryTiles(128, most_keys_first=True)
+# the mma.sync kernel of the general path (values of another size, capped scores): its tiles differ in
+# length by the causal mask alone, so the long ones go first and the short ones fill the end of the launch
+TILES_MMA_X = QueryTiles(64, most_keys_first=True)
 FORCED_SPLITS = int(os.environ.get("GOLLMGO_B200_DECODE_SPLITS", "0"))   # for measurements: this count, whatever the batch
 CTAS_PER_SM = 3            # decode attention CTAs resident on one SM (csrc/attention_mma.cu)
 TILE_KEYS = 64             # keys of one tile of the decode kernels
@@ -189,7 +192,7 @@ class Attention:
         need = [TILES_GENERAL]
         if self.general:
             if self._mma_x:
-                need.append(TILES_MMA)
+                need.append(TILES_MMA_X)
             return need
         if self.ctx.act_dtype == torch.bfloat16 and self.d in (64, 128) and ATTN_POLICY != "general":
             need.append(TILES_MMA)
@@ -291,7 +294,7 @@ class Attention:
             if TILES_GENERAL not in batch.tiles:
                 raise RuntimeError("the step's batch was built without the index lists this mixer declares in "
                                    "query_tiles(): give them to the BatchBuilder (query_tiles=...)")
-            t16, t64 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA) if self._mma_x else None
+            t16, t64 = batch.tiles[TILES_GENERAL], batch.tiles.get(TILES_MMA_X) if self._mma_x else None
             ops.attn_prefill_x(qkv, self.qkv_width, kc, vc, bt, batch.bt_stride, batch.cu_q_lens, batch.context_lens,
                                t16.seq, t16.q0, t16.count, out, self.nh, self.nkv, self.d, self.dv, self.v_share,
                                self.ctx.page_size, window, self.scale, self.softcap,
