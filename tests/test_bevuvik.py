@@ -191,7 +191,9 @@ def tagged(D, heads, d, scale, n_tags, tag_dim0, seed, boost=24.0):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(96, 4, 2, 32, 16, 16, 20.0, 16), (128, 6, 1, 24, 40, 0, 0.0, 8),
-                                   (160, 4, 4, 128, 128, 64, 30.0, 32), (104, 3, 3, 20, 12, 8, 12.0, 16)])
+                                   (160, 4, 4, 128, 128, 64, 30.0, 32), (104, 3, 3, 20, 12, 8, 12.0, 16),
+                                   (160, 4, 2, 128, 64, 32, 25.0, 16), (128, 4, 1, 64, 64, 16, 14.0, 8),
+                                   (128, 34, 1, 64, 128, 0, 0.0, 16)])
 def test_capped_attention_finds_one_key_among_hundreds(kit, dtype, shape):
     """Queries made to pick out single keys: the very first tokens, keys at both sides of page
     borders, keys hundreds of tokens back, a key that was itself decoded; asked for from prompt
